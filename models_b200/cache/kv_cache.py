@@ -34,12 +34,15 @@ class KvRequest:
     """What one attention-like mixer needs of the cache.  window None: every earlier position
     stays; n: only the n positions that end at the newest query.  `head_dim` is the size of a key
     head; a value head has `value_dim` (None: the same), as the reference's LayerSpec keeps keyDim and
-    valueDim apart (backend-java/.../cache/LayeredKvCache.java:35-64)."""
+    valueDim apart (backend-java/.../cache/LayeredKvCache.java:35-64).  `keep_first`: with a window, the
+    first so many positions of a sequence stay visible to every later query, so the pages that hold
+    them are never given back."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     value_dim: Optional[int] = None
+    keep_first: int = 0
 
     @property
     def value_head_dim(self) -> int:
@@ -82,7 +85,8 @@ class CacheGroup:
         first_visible = length - window + 1
         table = self.tables[slot]
         dropped = 0
-        for block in range(len(table)):
+        kept_blocks = -(-self.request.keep_first // self.page_size)  # pages with positions every later query sees
+        for block in range(kept_blocks, len(table)):
             if (block + 1) * self.page_size <= first_visible:
                 if table[block] >= 0:
                     self.pages.give_back(table[block])
@@ -175,7 +179,7 @@ class KvCache:
         if max_step_tokens <= 0:
             raise ValueError(f"max_step_tokens must be positive, got {max_step_tokens}")
         # positions a sequence holds at most while a step is in flight, wherever they start in a page
-        per_slot = -(-(request.window - 1 + max_step_tokens) // self.page_size) + 1
+        per_slot = -(-(request.window - 1 + max_step_tokens) // self.page_size) + 1 + -(-request.keep_first // self.page_size)
         return min(self.num_pages, self.max_slots * per_slot)
 
     def allocate_storage(self, allocate: Callable[[Tuple[int, ...]], object]) -> int:

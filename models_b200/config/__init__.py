@@ -1,3 +1,4 @@
+from .kabanex import KabanexConfig
 from .llama import ConfigError, LlamaConfig, RopeScalingConfig
 from .registry import (
     config_from_dict,
@@ -9,12 +10,18 @@ from .registry import (
 from .specs import (
     AttentionSpec,
     BlockSpec,
+    DenseFeedForwardSpec,
     EmbeddingSpec,
     GatedFeedForwardSpec,
     HeadSpec,
+    LayerNormSpec,
+    MinGruSpec,
     ModelSpec,
     NormSpec,
+    ParallelBlockSpec,
     RopeScalingSpec,
     RopeSpec,
     ScheduleEntry,
+    SideBySideSpec,
+    TalkingAttentionSpec,
 )

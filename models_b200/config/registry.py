@@ -11,6 +11,7 @@ import json
 from pathlib import Path
 from typing import Any, Callable, Dict, Mapping
 
+from .kabanex import ARCHITECTURE as KABANEX, KabanexConfig
 from .llama import ConfigError, LlamaConfig
 
 # name -> callable(raw config.json dict) -> object with .model_spec()
@@ -35,9 +36,13 @@ def known_architectures():
 
 def config_from_dict(raw: Mapping[str, Any]):
     architectures = raw.get("architectures")
-    if not architectures or not isinstance(architectures, (list, tuple)):
-        raise ConfigError("config.json: missing required key 'architectures' (a list whose first entry names the model)")
-    name = architectures[0]
+    if architectures and isinstance(architectures, (list, tuple)):
+        name = architectures[0]
+    elif isinstance(raw.get("architecture"), str):  # some formats name the model with one string
+        name = raw["architecture"]
+    else:
+        raise ConfigError("config.json: missing required key 'architectures' (a list whose first entry names the model; "
+                          "or 'architecture', one name)")
     if name not in _ARCHITECTURES:
         raise ConfigError(
             f"architecture {name!r} is not built; known architectures: {', '.join(known_architectures())}")
@@ -58,3 +63,4 @@ def load_config(folder):
 
 
 register_architecture("LlamaForCausalLM", LlamaConfig.from_dict)
+register_architecture(KABANEX, KabanexConfig.from_dict)

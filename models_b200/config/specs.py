@@ -70,6 +70,86 @@ class AttentionSpec:
 
 
 @dataclass(frozen=True)
+class LayerNormSpec:
+    """(x - mean) / sqrt(variance + eps) * weight + bias over the last axis; the variance is the mean of
+    the squared deviations from the mean."""
+
+    size: int
+    eps: float
+    weights: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+    kind: str = "layernorm"
+
+
+@dataclass(frozen=True)
+class TalkingAttentionSpec:
+    """Causal grouped-query attention whose softmax weights are mixed ACROSS heads before they meet the
+    values: w'_h(i, j) = sum_g talk[h, g] w_g(i, j); head h applies w'_h to the values of its own
+    key/value head.  Keys have `head_dim` coordinates and values `value_dim`.  Query i sees key j <= i
+    if i - j < `window` (None: no limit) or j < `keep_first` (the first positions of a sequence stay
+    visible to every later query, at their true positions).  `gated`: head h's result is multiplied by
+    sigmoid(gate_h . xn), one number per head and token, before the output matrix."""
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    position: Optional[RopeSpec]
+    window: Optional[int]
+    keep_first: int
+    gated: bool
+    weights: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+    kind: str = "talking_attention"
+
+
+@dataclass(frozen=True)
+class MinGruSpec:
+    """A gated recurrence whose gates read the current token only: z = sigmoid(Wz.xn + bz),
+    u = Wx.xn + bx, candidate c = u + 1/2 where u >= 0 and sigmoid(u) elsewhere,
+    S_t = (1 - z) S_(t-1) + z c element by element, result Wo.(S_t * silu(Wg.xn)).  The state is
+    `state_size` float32 numbers per sequence and starts at zero."""
+
+    hidden_size: int
+    state_size: int
+    weights: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+    kind: str = "mingru"
+
+
+@dataclass(frozen=True)
+class SideBySideSpec:
+    """Two mixers that read the same rows; the result is left_scale * left + right_scale * right."""
+
+    left: object
+    right: object
+    left_scale: float
+    right_scale: float
+    kind: str = "side_by_side"
+
+
+@dataclass(frozen=True)
+class DenseFeedForwardSpec:
+    """down(act(up(x))), no gate.  activation: a name of the activation table ("relu2": relu squared)."""
+
+    hidden_size: int
+    intermediate_size: int
+    activation: str
+    weights: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+    kind: str = "dense"
+
+
+@dataclass(frozen=True)
+class ParallelBlockSpec:
+    """One layer with ONE norm whose rows both sublayers read: h = norm(x); x += mixer(h) + feed_forward(h).
+    `feed_forward` None: the layer has only the mixer."""
+
+    mixer: object
+    feed_forward: Optional[object]
+    norm: object
+    kind: str = "parallel"
+
+
+@dataclass(frozen=True)
 class GatedFeedForwardSpec:
     """down(act(gate(x)) * up(x)), dense."""
 

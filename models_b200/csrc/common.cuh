@@ -19,14 +19,19 @@
 // epilogue argument (0, the default, is SiLU).
 #define MB_ACT_SILU 0
 #define MB_ACT_GELU_TANH 1
-#define MB_ACT_COUNT 2
+#define MB_ACT_RELU2 2
+#define MB_ACT_COUNT 3
 
 namespace mb {
 
 // act(gate): silu(z) = z / (1 + exp(-z)) (integrallis/models, backend-java/.../ops/TensorOps.java:1407-1425);
-// gelu_tanh(z) = 0.5 z (1 + tanh(0.7978845608 z (1 + 0.044715 z^2))) (:1427-1449).  `activation` is the
-// same for every thread of a launch, so the branch does not diverge.
+// gelu_tanh(z) = 0.5 z (1 + tanh(0.7978845608 z (1 + 0.044715 z^2))) (:1427-1449); relu2(z) = max(z, 0)^2.
+// `activation` is the same for every thread of a launch, so the branch does not diverge.
 __device__ __forceinline__ float gate_activation(int activation, float z) {
+    if (activation == MB_ACT_RELU2) {
+        const float r = fmaxf(z, 0.0f);
+        return r * r;
+    }
     if (activation == MB_ACT_GELU_TANH)
         return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * z * (1.0f + 0.044715f * z * z)));
     return z / (1.0f + expf(-z));

@@ -332,6 +332,36 @@ inline int grid_for(size_t total, int block) {
     return (int)(blocks > 148 * 16 ? 148 * 16 : (blocks ? blocks : 1));
 }
 
+// One block per output row.  Two walks: the mean, then the mean of the squared deviations from it.
+template <typename Out>
+__global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ weight, const float* __restrict__ bias,
+                                 Out* __restrict__ out, const int* __restrict__ rows, int width, float eps) {
+    __shared__ float scratch[32];
+    const int source = rows != nullptr ? rows[blockIdx.x] : blockIdx.x;
+    const float* row = x + (size_t)source * width;
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) sum += row[i];
+    const float mean = block_sum(sum, scratch) / (float)width;
+    float squares = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float d = row[i] - mean;
+        squares = fmaf(d, d, squares);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(squares, scratch) / (float)width + eps);
+    Out* out_row = out + (size_t)blockIdx.x * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        Num<Out>::store(out_row + i, (row[i] - mean) * inv * weight[i] + bias[i]);
+}
+
+template <typename T>
+__global__ void activate_kernel(const T* __restrict__ src, int src_stride, T* __restrict__ dst, int dst_stride, int cols,
+                                size_t total, int activation, float scale) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / cols, c = i % cols;
+        Num<T>::store(dst + r * dst_stride + c, scale * gate_activation(activation, Num<T>::load(src + r * src_stride + c)));
+    }
+}
+
 }  // namespace mb
 
 using namespace mb;
@@ -449,6 +479,40 @@ MB_EXPORT int mb_rope_cache_write(void* qkv, int dtype, int row_stride, const in
                                 (__nv_bfloat16*)v_pool, slot_mapping, heads, kv_heads, head_dim, rotary_dim, interleaved, page_size,
                                 write_cache);
     return fail("rope_cache_write: unknown dtype code %d", dtype);
+}
+
+// Layer norm of float rows: (x - mean) / sqrt(var + eps) * weight + bias, var the mean of the squared deviations
+// from the mean (two walks over the row, so nothing is lost to cancellation).  `rows` (or null) gathers.
+MB_EXPORT int mb_layernorm(const float* x, const float* weight, const float* bias, void* out, int out_dtype, const int* rows,
+                           int out_rows, int width, float eps, cudaStream_t stream) {
+    if (out_rows <= 0 || width <= 0) return 0;
+    const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
+    if (out_dtype == MB_F32)
+        layernorm_kernel<float><<<out_rows, threads, 0, stream>>>(x, weight, bias, (float*)out, rows, width, eps);
+    else if (out_dtype == MB_BF16)
+        layernorm_kernel<__nv_bfloat16><<<out_rows, threads, 0, stream>>>(x, weight, bias, (__nv_bfloat16*)out, rows, width, eps);
+    else
+        return fail("layernorm: unknown dtype code %d", out_dtype);
+    return check_launch("layernorm");
+}
+
+// dst[r, c] = scale * act(src[r, c]) for [rows, cols] column slices with row strides (in elements); activation: MB_ACT_*.
+MB_EXPORT int mb_activate(const void* src, int src_stride, void* dst, int dst_stride, int dtype, int rows, int cols,
+                          int activation, float scale, cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return 0;
+    if (activation < 0 || activation >= MB_ACT_COUNT) return fail("activate: unknown activation code %d", activation);
+    const size_t total = (size_t)rows * cols;
+    const size_t blocks = (total + 255) / 256;
+    const int grid = (int)(blocks > 148 * 32 ? 148 * 32 : blocks);
+    if (dtype == MB_F32)
+        activate_kernel<float><<<grid, 256, 0, stream>>>((const float*)src, src_stride, (float*)dst, dst_stride, cols, total,
+                                                       activation, scale);
+    else if (dtype == MB_BF16)
+        activate_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)src, src_stride, (__nv_bfloat16*)dst,
+                                                               dst_stride, cols, total, activation, scale);
+    else
+        return fail("activate: unknown dtype code %d", dtype);
+    return check_launch("activate");
 }
 
 // out [rows, width] = act(gate) * up for gate_up [rows, 2 * width]; activation: MB_ACT_*.

@@ -1,0 +1,103 @@
+// Element-wise gated recurrences over the tokens of ragged sequences, with the state of every sequence
+// kept in float between steps.
+//
+// minGRU (gates read the current token only):
+//   z_t = sigmoid(zin_t + bz)          u_t = xin_t + bx
+//   c_t = u_t + 1/2 where u_t >= 0, sigmoid(u_t) elsewhere
+//   S_t = (1 - z_t) S_(t-1) + z_t c_t
+//   y_t = out_scale * S_t * silu(gin_t)
+// zin, xin, gin are projections of the token (storage type, float or bfloat16); everything after them is float.
+//
+// The recurrence is linear in S, so a step of many tokens is cut into `chunks` runs of consecutive tokens
+// that are walked at the same time: each run first finds its own (A, B) with S_end = A S_start + B, the
+// starts follow from the sequence's stored state by composing the runs before, and a second walk writes
+// the results.  With one token per sequence (decoding) there is one run and one walk.
+#include "common.cuh"
+
+MB_DEFINE_LAST_ERROR()
+
+namespace mb {
+
+constexpr int kChannels = 32;
+constexpr int kMaxChunks = 32;
+
+__device__ __forceinline__ float sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
+
+// grid (ceil(width / 32), sequences); block (32, chunks).
+template <typename T>
+__global__ void mingru_scan_kernel(const T* __restrict__ zin, const T* __restrict__ xin, const T* __restrict__ gin,
+                                   int in_stride, const float* __restrict__ z_bias, const float* __restrict__ x_bias,
+                                   float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu_q,
+                                   int width, T* __restrict__ out, int out_stride, float out_scale) {
+    __shared__ float a_of[kMaxChunks][kChannels];
+    __shared__ float b_of[kMaxChunks][kChannels];
+    const int seq = blockIdx.y;
+    const int first = cu_q[seq];
+    const int count = cu_q[seq + 1] - first;
+    if (count <= 0) return;  // the whole block leaves
+    const int channel = blockIdx.x * kChannels + threadIdx.x;
+    const bool live = channel < width;
+    const int chunks = blockDim.y, chunk = threadIdx.y;
+    const int per = (count + chunks - 1) / chunks;
+    const int t0 = min(chunk * per, count), t1 = min(t0 + per, count);
+    const float bz = live ? z_bias[channel] : 0.0f, bx = live ? x_bias[channel] : 0.0f;
+
+    if (chunks > 1) {
+        float a = 1.0f, b = 0.0f;
+        if (live) {
+            for (int t = t0; t < t1; ++t) {
+                const size_t at = (size_t)(first + t) * in_stride + channel;
+                const float z = sigmoid(Num<T>::load(zin + at) + bz);
+                const float u = Num<T>::load(xin + at) + bx;
+                const float c = u >= 0.0f ? u + 0.5f : sigmoid(u);
+                a *= 1.0f - z;
+                b = (1.0f - z) * b + z * c;
+            }
+        }
+        a_of[chunk][threadIdx.x] = a;
+        b_of[chunk][threadIdx.x] = b;
+        __syncthreads();
+    }
+    if (!live) return;
+    float* stored = state + (size_t)slots[seq] * width + channel;
+    float s = *stored;
+    for (int before = 0; before < chunk; ++before) s = a_of[before][threadIdx.x] * s + b_of[before][threadIdx.x];
+    for (int t = t0; t < t1; ++t) {
+        const size_t at = (size_t)(first + t) * in_stride + channel;
+        const float z = sigmoid(Num<T>::load(zin + at) + bz);
+        const float u = Num<T>::load(xin + at) + bx;
+        const float c = u >= 0.0f ? u + 0.5f : sigmoid(u);
+        s = (1.0f - z) * s + z * c;
+        const float g = Num<T>::load(gin + at);
+        Num<T>::store(out + (size_t)(first + t) * out_stride + channel, out_scale * s * (g * sigmoid(g)));
+    }
+    if (chunk == chunks - 1) *stored = s;  // runs after the last token are empty: this is the state after all of them
+}
+
+}  // namespace mb
+
+using namespace mb;
+
+// zin, xin, gin: [tokens, >= width] rows of the storage type with one row stride (column slices of one
+// tensor); out likewise with its own stride.  state: float [slots, width]; slots[sequence] picks the row.
+MB_EXPORT int mb_mingru_scan(const void* zin, const void* xin, const void* gin, int in_stride, int dtype,
+                             const float* z_bias, const float* x_bias, float* state, const int* slots, const int* cu_q,
+                             int sequences, int max_q_len, int width, void* out, int out_stride, float out_scale,
+                             cudaStream_t stream) {
+    if (sequences <= 0 || max_q_len <= 0 || width <= 0) return 0;
+    if (sequences > 65535) return fail("mingru_scan: %d sequences exceed the grid limit 65535", sequences);
+    int chunks = 1;
+    while (chunks < kMaxChunks && chunks * 8 < max_q_len) chunks *= 2;  // runs of at least 8 tokens
+    const dim3 grid((width + kChannels - 1) / kChannels, sequences), block(kChannels, chunks);
+    if (dtype == MB_F32)
+        mingru_scan_kernel<float><<<grid, block, 0, stream>>>((const float*)zin, (const float*)xin, (const float*)gin, in_stride,
+                                                            z_bias, x_bias, state, slots, cu_q, width, (float*)out,
+                                                            out_stride, out_scale);
+    else if (dtype == MB_BF16)
+        mingru_scan_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(
+            (const __nv_bfloat16*)zin, (const __nv_bfloat16*)xin, (const __nv_bfloat16*)gin, in_stride, z_bias, x_bias, state,
+            slots, cu_q, width, (__nv_bfloat16*)out, out_stride, out_scale);
+    else
+        return fail("mingru_scan: unknown dtype code %d", dtype);
+    return check_launch("mingru_scan");
+}

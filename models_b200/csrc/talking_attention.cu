@@ -1,0 +1,314 @@
+// Attention whose softmax weights are mixed across heads ("talking heads"), over a paged cache with a
+// sliding window that also keeps the first positions of a sequence, with key and value heads of
+// different sizes and an optional per-head output gate.  Float or bfloat16 storage; scores, weights,
+// the mixing and the sums over keys are float in both.
+//
+//   s_g(i, j) = scale * q_g(i) . k_c(j)                 c = g / (heads / kv_heads)
+//   visible(i, j): j <= i and (i - j < window or j < keep_first)        (window 0: every j <= i)
+//   w_g(i, .) = softmax over the visible j of s_g(i, .)
+//   w'_h(i, j) = sum_g talk[h, g] w_g(i, j)             (talk absent: w' = w)
+//   out_h(i) = out_scale * gate_h(i) * sum_j w'_h(i, j) v_c(j)          c = h / (heads / kv_heads)
+//   gate_h(i) = 1 / (1 + exp(-gate_in[i, h]))           (gate_in absent: 1)
+//
+// Mixing needs every head's NORMALISED weight of a key at once, so a block owns one query token with all
+// its heads and walks the visible keys twice: the first walk finds each head's maximum and sum, the
+// second recomputes the scores, normalises them, mixes them across heads in shared memory and applies
+// them to the values.  Keys are walked in chunks of 32 positions (a chunk lies within one cache page).
+//
+// Cache layout of one layer: k_pool[page][kv_head][page_size][head_dim],
+// v_pool[page][kv_head][page_size][value_dim]; block_table[seq][i] is the page that holds positions
+// [i*page_size, (i+1)*page_size) of that sequence.  Pages that hold only invisible positions are never read.
+#include "common.cuh"
+
+#include <math_constants.h>
+
+MB_DEFINE_LAST_ERROR()
+
+namespace mb {
+
+constexpr int kChunk = 32;
+constexpr int kMaxAcc = 16;  // outputs per thread: heads * value_dim <= kMaxAcc * threads
+constexpr int kMaxThreads = 512;
+
+template <typename T>
+__device__ __forceinline__ float dot_row(const float* __restrict__ q_shared, const T* __restrict__ k_row, int head_dim,
+                                         bool vector_ok) {
+    float sum = 0.0f;
+    if (vector_ok) {
+        for (int d = 0; d < head_dim; d += 8) {
+            float kv[8];
+            load8(k_row + d, kv);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sum = fmaf(q_shared[d + i], kv[i], sum);
+        }
+    } else {
+        for (int d = 0; d < head_dim; ++d) sum = fmaf(q_shared[d], Num<T>::load(k_row + d), sum);
+    }
+    return sum;
+}
+
+// Rotation of query and key heads (split-half pairs over the first rotary_dim coordinates, angles from
+// the tables) and the cache write: keys rotated, values as they are.  q is rotated in place.
+// grid (tokens); any block size.
+template <typename T>
+__global__ void rotate_store_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride,
+                                    const T* __restrict__ v, int v_stride, const int* __restrict__ positions,
+                                    const float* __restrict__ cos_table, const float* __restrict__ sin_table,
+                                    T* __restrict__ k_pool, T* __restrict__ v_pool, const int* __restrict__ slot_mapping,
+                                    int heads, int kv_heads, int head_dim, int value_dim, int rotary_dim, int page_size) {
+    const int token = blockIdx.x;
+    const int half = rotary_dim / 2;
+    const int pos = positions[token];
+    const float* cos_row = cos_table + (size_t)pos * half;
+    const float* sin_row = sin_table + (size_t)pos * half;
+    T* q_row = q + (size_t)token * q_stride;
+    for (int item = threadIdx.x; item < heads * half; item += blockDim.x) {
+        const int head = item / half, i = item % half;
+        T* p = q_row + (size_t)head * head_dim;
+        const float a = Num<T>::load(p + i), b = Num<T>::load(p + i + half);
+        const float c = cos_row[i], s = sin_row[i];
+        Num<T>::store(p + i, a * c - b * s);
+        Num<T>::store(p + i + half, b * c + a * s);
+    }
+    const int slot = slot_mapping[token];
+    if (slot < 0) return;  // a padding row stores nothing
+    const size_t page = slot / page_size, offset = slot % page_size;
+    const T* k_row = k + (size_t)token * k_stride;
+    for (int item = threadIdx.x; item < kv_heads * head_dim; item += blockDim.x) {
+        const int head = item / head_dim, d = item % head_dim;
+        const T* p = k_row + (size_t)head * head_dim;
+        float value;
+        if (d < half) {
+            value = Num<T>::load(p + d) * cos_row[d] - Num<T>::load(p + d + half) * sin_row[d];
+        } else if (d < rotary_dim) {
+            const int i = d - half;
+            value = Num<T>::load(p + d) * cos_row[i] + Num<T>::load(p + i) * sin_row[i];
+        } else {
+            value = Num<T>::load(p + d);
+        }
+        Num<T>::store(k_pool + ((page * kv_heads + head) * page_size + offset) * head_dim + d, value);
+    }
+    const T* v_row = v + (size_t)token * v_stride;
+    for (int item = threadIdx.x; item < kv_heads * value_dim; item += blockDim.x) {
+        const int head = item / value_dim, d = item % value_dim;
+        v_pool[((page * kv_heads + head) * page_size + offset) * value_dim + d] = v_row[(size_t)head * value_dim + d];
+    }
+}
+
+// grid (max_q_len, sequences); block: a multiple of 32 threads with heads * value_dim <= kMaxAcc * threads.
+// shared: q [heads * head_dim], weights [heads][32], mixed [heads][32], maxima [heads], sums [heads], talk [heads^2].
+template <typename T>
+__global__ void __launch_bounds__(kMaxThreads) talking_attention_rows_kernel(
+    const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride, const T* __restrict__ k_pool,
+    const T* __restrict__ v_pool, const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
+    const int* __restrict__ kv_lens, const float* __restrict__ talk, const T* __restrict__ gate_in, int gate_stride,
+    int heads, int kv_heads, int head_dim, int value_dim, int page_size, int window, int keep_first, float scale,
+    float out_scale) {
+    extern __shared__ float shared[];
+    const int seq = blockIdx.y;
+    const int q_begin = cu_q[seq];
+    const int q_len = cu_q[seq + 1] - q_begin;
+    const int j = blockIdx.x;
+    if (j >= q_len) return;  // the whole block leaves
+    const int row = q_begin + j;
+    const int pos = kv_lens[seq] - q_len + j;
+    const int window_first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int kept_end = keep_first < window_first ? keep_first : window_first;  // [0, kept_end): kept first positions
+    const int group = heads / kv_heads;
+    const bool vector_ok = (head_dim % 8) == 0;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+
+    float* q_shared = shared;
+    float* weights = q_shared + heads * head_dim;
+    float* mixed = weights + heads * kChunk;
+    float* maxima = mixed + heads * kChunk;
+    float* sums = maxima + heads;
+    float* talk_shared = sums + heads;
+
+    const T* q_row = q + (size_t)row * q_stride;
+    for (int i = threadIdx.x; i < heads * head_dim; i += blockDim.x) q_shared[i] = Num<T>::load(q_row + i);
+    if (talk != nullptr)
+        for (int i = threadIdx.x; i < heads * heads; i += blockDim.x) talk_shared[i] = talk[i];
+    __syncthreads();
+    const int* table = block_table + (size_t)seq * max_blocks;
+
+    // first walk: every head's maximum and sum of exponentials over the visible keys (a warp owns a head)
+    for (int head = warp; head < heads; head += warps) {
+        const int kv_head = head / group;
+        float running_max = -CUDART_INF_F, running_sum = 0.0f;
+        for (int range = 0; range < 2; ++range) {
+            const int begin = range == 0 ? 0 : window_first, end = range == 0 ? kept_end : pos + 1;
+            for (int chunk = begin - begin % kChunk; chunk < end; chunk += kChunk) {
+                const size_t page = table[chunk / page_size];
+                const size_t base = (page * kv_heads + kv_head) * page_size + (chunk % page_size);
+                const int p = chunk + lane;
+                float score = -CUDART_INF_F;
+                if (p >= begin && p < end)
+                    score = dot_row<T>(q_shared + head * head_dim, k_pool + (base + lane) * head_dim, head_dim, vector_ok) * scale;
+                const float new_max = fmaxf(running_max, warp_max(score));  // finite: the chunk holds a visible key
+                const float e = expf(score - new_max);                      // exp(-inf) = 0 for an invisible key
+                running_sum = running_sum * expf(running_max - new_max) + warp_sum(e);
+                running_max = new_max;
+            }
+        }
+        if (lane == 0) {
+            maxima[head] = running_max;
+            sums[head] = running_sum;
+        }
+    }
+    __syncthreads();
+
+    float acc[kMaxAcc];
+#pragma unroll
+    for (int i = 0; i < kMaxAcc; ++i) acc[i] = 0.0f;
+    const int outputs = heads * value_dim;
+
+    // second walk: normalised weights of a chunk for all heads, mixed across heads, applied to the values
+    for (int range = 0; range < 2; ++range) {
+        const int begin = range == 0 ? 0 : window_first, end = range == 0 ? kept_end : pos + 1;
+        for (int chunk = begin - begin % kChunk; chunk < end; chunk += kChunk) {
+            const size_t page = table[chunk / page_size];
+            const size_t page_base = page * kv_heads * page_size + (chunk % page_size);
+            for (int head = warp; head < heads; head += warps) {
+                const size_t base = page_base + (size_t)(head / group) * page_size;
+                const int p = chunk + lane;
+                float weight = 0.0f;
+                if (p >= begin && p < end) {
+                    const float score =
+                        dot_row<T>(q_shared + head * head_dim, k_pool + (base + lane) * head_dim, head_dim, vector_ok) * scale;
+                    weight = expf(score - maxima[head]) / sums[head];
+                }
+                weights[head * kChunk + lane] = weight;
+            }
+            __syncthreads();
+            const float* applied = weights;
+            if (talk != nullptr) {
+                for (int item = threadIdx.x; item < heads * kChunk; item += blockDim.x) {
+                    const int head = item / kChunk, key = item % kChunk;
+                    float sum = 0.0f;
+                    for (int g = 0; g < heads; ++g) sum = fmaf(talk_shared[head * heads + g], weights[g * kChunk + key], sum);
+                    mixed[item] = sum;
+                }
+                __syncthreads();
+                applied = mixed;
+            }
+            const int first_key = begin > chunk ? begin - chunk : 0;
+            const int last_key = end - chunk < kChunk ? end - chunk : kChunk;
+#pragma unroll
+            for (int i = 0; i < kMaxAcc; ++i) {
+                const int o = threadIdx.x + i * blockDim.x;
+                if (o < outputs) {
+                    const int head = o / value_dim, d = o % value_dim;
+                    const T* v_col = v_pool + (page_base + (size_t)(head / group) * page_size) * value_dim + d;
+                    const float* w = applied + head * kChunk;
+                    float sum = acc[i];
+                    for (int key = first_key; key < last_key; ++key)
+                        sum = fmaf(w[key], Num<T>::load(v_col + (size_t)key * value_dim), sum);
+                    acc[i] = sum;
+                }
+            }
+            __syncthreads();  // the next chunk overwrites the weights
+        }
+    }
+
+    T* out_row = out + (size_t)row * out_stride;
+#pragma unroll
+    for (int i = 0; i < kMaxAcc; ++i) {
+        const int o = threadIdx.x + i * blockDim.x;
+        if (o < outputs) {
+            float value = acc[i] * out_scale;
+            if (gate_in != nullptr) {
+                const float z = Num<T>::load(gate_in + (size_t)row * gate_stride + o / value_dim);
+                value *= 1.0f / (1.0f + expf(-z));
+            }
+            Num<T>::store(out_row + o, value);
+        }
+    }
+}
+
+}  // namespace mb
+
+using namespace mb;
+
+// q (rotated in place), k, v: [tokens, ...] rows with unit column stride and the row strides given (in
+// elements); they may be column slices of one wider tensor.  slot_mapping[token]: page * page_size +
+// offset of the token's cache position, or -1 for a row that stores nothing.
+MB_EXPORT int mb_rotate_store(void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, int dtype,
+                              const int* positions, const float* cos_table, const float* sin_table, void* k_pool,
+                              void* v_pool, const int* slot_mapping, int tokens, int heads, int kv_heads, int head_dim,
+                              int value_dim, int rotary_dim, int page_size, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1))
+        return fail("rotate_store: rotary_dim %d must be even and at most head_dim %d", rotary_dim, head_dim);
+    if (rotary_dim > 0 && (!cos_table || !sin_table || !positions))
+        return fail("rotate_store: a rotation needs positions and cos/sin tables");
+    if (!k_pool || !v_pool || !slot_mapping || page_size <= 0)
+        return fail("rotate_store: needs pools, a slot mapping and a page size");
+    if (rotary_dim == 0) {  // the tables are not read; any valid address serves
+        cos_table = sin_table = reinterpret_cast<const float*>(slot_mapping);
+    }
+    const int work = kv_heads * (head_dim > value_dim ? head_dim : value_dim);
+    const int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
+    if (dtype == MB_F32)
+        rotate_store_kernel<float><<<tokens, threads, 0, stream>>>(
+            (float*)q, q_stride, (const float*)k, k_stride, (const float*)v, v_stride, positions, cos_table, sin_table,
+            (float*)k_pool, (float*)v_pool, slot_mapping, heads, kv_heads, head_dim, value_dim, rotary_dim, page_size);
+    else if (dtype == MB_BF16)
+        rotate_store_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(
+            (__nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, positions,
+            cos_table, sin_table, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, slot_mapping, heads, kv_heads, head_dim,
+            value_dim, rotary_dim, page_size);
+    else
+        return fail("rotate_store: unknown dtype code %d", dtype);
+    return check_launch("rotate_store");
+}
+
+// q: [tokens, >= heads*head_dim] rows (row stride in elements); out: [tokens, >= heads*value_dim] rows.
+// talk: float [heads, heads] or null; gate_in: [tokens, >= heads] rows of the storage type, or null.
+MB_EXPORT int mb_talking_attention_rows(const void* q, int q_stride, void* out, int out_stride, int dtype, const void* k_pool,
+                                        const void* v_pool, const int* block_table, int max_blocks, const int* cu_q,
+                                        const int* kv_lens, int sequences, int max_q_len, const float* talk,
+                                        const void* gate_in, int gate_stride, int heads, int kv_heads, int head_dim,
+                                        int value_dim, int page_size, int window, int keep_first, float scale,
+                                        float out_scale, cudaStream_t stream) {
+    if (sequences <= 0 || max_q_len <= 0) return 0;
+    if (heads <= 0 || kv_heads <= 0 || heads % kv_heads)
+        return fail("talking_attention: %d heads are no multiple of %d kv heads", heads, kv_heads);
+    if (head_dim <= 0 || value_dim <= 0) return fail("talking_attention: head sizes must be positive");
+    if (page_size <= 0 || page_size % kChunk) return fail("talking_attention: page_size %d must be a multiple of %d", page_size, kChunk);
+    if (window < 0 || keep_first < 0) return fail("talking_attention: window and keep_first must not be negative");
+    if (sequences > 65535) return fail("talking_attention: %d sequences exceed the grid limit 65535", sequences);
+    const int outputs = heads * value_dim;
+    int threads = 128;
+    while (threads < kMaxThreads && (threads * kMaxAcc < outputs || (threads < 32 * heads && threads < 256))) threads *= 2;
+    if (threads * kMaxAcc < outputs)
+        return fail("talking_attention: heads * value_dim = %d exceeds %d", outputs, kMaxThreads * kMaxAcc);
+    const size_t smem = sizeof(float) * ((size_t)heads * head_dim + 2 * (size_t)heads * kChunk + 2 * heads + (size_t)heads * heads);
+    if (smem > 200 * 1024) return fail("talking_attention: %d heads of %d do not fit a block's shared memory", heads, head_dim);
+    const dim3 grid(max_q_len, sequences);
+    cudaError_t status;
+    if (dtype == MB_F32) {
+        auto kernel = talking_attention_rows_kernel<float>;
+        if (smem > 48 * 1024) {
+            status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (status != cudaSuccess) return fail("talking_attention: %s", cudaGetErrorString(status));
+        }
+        kernel<<<grid, threads, smem, stream>>>(
+            (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_pool, (const float*)v_pool, block_table,
+            max_blocks, cu_q, kv_lens, talk, (const float*)gate_in, gate_stride, heads, kv_heads, head_dim, value_dim,
+            page_size, window, keep_first, scale, out_scale);
+    } else if (dtype == MB_BF16) {
+        auto kernel = talking_attention_rows_kernel<__nv_bfloat16>;
+        if (smem > 48 * 1024) {
+            status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (status != cudaSuccess) return fail("talking_attention: %s", cudaGetErrorString(status));
+        }
+        kernel<<<grid, threads, smem, stream>>>(
+            (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool,
+            (const __nv_bfloat16*)v_pool, block_table, max_blocks, cu_q, kv_lens, talk, (const __nv_bfloat16*)gate_in,
+            gate_stride, heads, kv_heads, head_dim, value_dim, page_size, window, keep_first, scale, out_scale);
+    } else {
+        return fail("talking_attention: unknown dtype code %d", dtype);
+    }
+    return check_launch("talking_attention");
+}

@@ -212,7 +212,7 @@ def rope_cache_write(qkv: torch.Tensor, positions: Optional[torch.Tensor], cos: 
                                       1 if write_cache else 0, _stream()))
 
 
-ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}  # the codes of csrc/common.cuh (MB_ACT_*)
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu2": 2}  # the codes of csrc/common.cuh (MB_ACT_*)
 
 
 def activation_code(activation: str) -> int:
@@ -269,6 +269,44 @@ def residual_add(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
     return x
 
 
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float, out_dtype: torch.dtype,
+              rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Layer norm with gain and bias of the float residual rows x [T, width] (of the rows picked by `rows`,
+    if given): mean, variance and the result in float, stored as `out_dtype`."""
+    _cuda(x, weight, bias, rows)
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous():
+        raise KernelError("the residual stream must be a contiguous float32 [rows, width] tensor")
+    width = x.shape[1]
+    for name, t in (("weight", weight), ("bias", bias)):
+        if t.dtype != torch.float32 or t.numel() != width or not t.is_contiguous():
+            raise KernelError(f"layer norm {name} must be contiguous float32 of {width} elements")
+    _int32(rows, "rows")
+    out_rows = rows.numel() if rows is not None else x.shape[0]
+    out = torch.empty((out_rows, width), dtype=out_dtype, device=x.device)
+    lib = elementwise()
+    _run(lib, lib.mb_layernorm(_p(x), _p(weight), _p(bias), _p(out), _code(out_dtype), _p(rows), out_rows, width,
+                               ctypes.c_float(eps), _stream()))
+    return out
+
+
+def _columns(t: torch.Tensor, name: str):
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{name} must be a [rows, columns] tensor (or column slice) with unit column stride")
+
+
+def activate(src: torch.Tensor, dst: torch.Tensor, activation: str, scale: float = 1.0) -> torch.Tensor:
+    """dst = scale * act(src), element by element; both may be column slices of wider tensors."""
+    _cuda(src, dst)
+    _columns(src, "src")
+    _columns(dst, "dst")
+    if src.shape != dst.shape or src.dtype != dst.dtype:
+        raise KernelError(f"activate: {tuple(src.shape)} {src.dtype} does not fit {tuple(dst.shape)} {dst.dtype}")
+    lib = elementwise()
+    _run(lib, lib.mb_activate(_p(src), src.stride(0), _p(dst), dst.stride(0), _code(src.dtype), src.shape[0], src.shape[1],
+                              activation_code(activation), ctypes.c_float(scale), _stream()))
+    return dst
+
+
 # ------------------------------------------------------------------------------------ attention
 
 def paged_attention_rows(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
@@ -294,6 +332,109 @@ def paged_attention_rows(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tenso
                                           _p(v_pool), _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_lens),
                                           sequences, max_q_len, heads, kv_heads, head_dim, k_pool.shape[2],
                                           window or 0, ctypes.c_float(scale), _stream()))
+
+
+def talking_attention_library():
+    return load_library("mb_talking_attention", ["talking_attention.cu"])
+
+
+def rotate_store(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, positions: torch.Tensor, cos: Optional[torch.Tensor],
+                 sin: Optional[torch.Tensor], k_pool: torch.Tensor, v_pool: torch.Tensor, slot_mapping: torch.Tensor,
+                 heads: int, kv_heads: int, head_dim: int, value_dim: int, rotary_dim: int) -> None:
+    """Rotates the query heads of q ([T, heads*head_dim], in place) and the key heads of k by the tables
+    (split-half pairs over the first `rotary_dim` coordinates; 0: none), and stores keys and values (value
+    heads of `value_dim`) in the pools at `slot_mapping`.  q, k and v may be column slices of one tensor."""
+    _cuda(q, k, v, positions, cos, sin, k_pool, v_pool, slot_mapping)
+    for name, t, width in (("q", q, heads * head_dim), ("k", k, kv_heads * head_dim), ("v", v, kv_heads * value_dim)):
+        _columns(t, name)
+        if t.shape[1] != width or t.shape[0] != q.shape[0]:
+            raise KernelError(f"rotate_store: {name} is {tuple(t.shape)}, {width} columns are needed")
+    _int32(positions, "positions")
+    _int32(slot_mapping, "slot_mapping")
+    if rotary_dim > 0:
+        if cos is None or sin is None or cos.dtype != torch.float32 or sin.dtype != torch.float32:
+            raise KernelError("rotation needs float32 cos/sin tables")
+        if cos.shape[-1] != rotary_dim // 2 or cos.shape != sin.shape or not cos.is_contiguous() or not sin.is_contiguous():
+            raise KernelError(f"cos/sin tables must be contiguous [positions, {rotary_dim // 2}]")
+    if not (q.dtype == k.dtype == v.dtype == k_pool.dtype == v_pool.dtype):
+        raise KernelError("q, k, v and the cache pools must share one dtype")
+    page_size = k_pool.shape[2]
+    if (tuple(k_pool.shape[1:]) != (kv_heads, page_size, head_dim) or tuple(v_pool.shape[1:]) != (kv_heads, page_size, value_dim)
+            or not k_pool.is_contiguous() or not v_pool.is_contiguous()):
+        raise KernelError(f"pools must be contiguous [pages, {kv_heads}, page_size, {head_dim}] and [.., {value_dim}]")
+    lib = talking_attention_library()
+    _run(lib, lib.mb_rotate_store(_p(q), q.stride(0), _p(k), k.stride(0), _p(v), v.stride(0), _code(q.dtype), _p(positions),
+                                  _p(cos), _p(sin), _p(k_pool), _p(v_pool), _p(slot_mapping), q.shape[0], heads, kv_heads,
+                                  head_dim, value_dim, rotary_dim, page_size, _stream()))
+
+
+def talking_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                      block_table: torch.Tensor, cu_q: torch.Tensor, kv_lens: torch.Tensor, max_q_len: int, heads: int,
+                      kv_heads: int, head_dim: int, value_dim: int, window: Optional[int], keep_first: int, scale: float,
+                      talk: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, out_scale: float = 1.0) -> None:
+    """Causal attention over the paged cache with softmax weights mixed across heads by `talk` (float32
+    [heads, heads]; None: not mixed), a window that also keeps the first `keep_first` positions, value heads
+    of `value_dim`, and an output gate: out_h = out_scale * sigmoid(gate[:, h]) * sum_j w'_h(j) v(j).
+    q [T, heads*head_dim], out [T, heads*value_dim], gate [T, heads] (or None) may be column slices."""
+    _cuda(q, out, k_pool, v_pool, block_table, cu_q, kv_lens, talk, gate)
+    _int32(block_table, "block_table")
+    _int32(cu_q, "cu_q")
+    _int32(kv_lens, "kv_lens")
+    _columns(q, "q")
+    _columns(out, "out")
+    if q.shape[1] != heads * head_dim or out.shape[1] != heads * value_dim or q.shape[0] != out.shape[0]:
+        raise KernelError(f"talking_attention: q {tuple(q.shape)} and out {tuple(out.shape)} do not fit {heads} heads of "
+                          f"{head_dim} and {value_dim}")
+    page_size = k_pool.shape[2]
+    if (tuple(k_pool.shape[1:]) != (kv_heads, page_size, head_dim) or tuple(v_pool.shape[1:]) != (kv_heads, page_size, value_dim)
+            or not k_pool.is_contiguous() or not v_pool.is_contiguous()):
+        raise KernelError(f"pools must be contiguous [pages, {kv_heads}, page_size, {head_dim}] and [.., {value_dim}]")
+    if not (q.dtype == out.dtype == k_pool.dtype == v_pool.dtype):
+        raise KernelError("q, out and the pools must share one dtype")
+    if talk is not None and (talk.dtype != torch.float32 or tuple(talk.shape) != (heads, heads) or not talk.is_contiguous()):
+        raise KernelError(f"talk must be a contiguous float32 [{heads}, {heads}] matrix")
+    if gate is not None:
+        _columns(gate, "gate")
+        if gate.dtype != q.dtype or tuple(gate.shape) != (q.shape[0], heads):
+            raise KernelError(f"gate must be [{q.shape[0]}, {heads}] of q's dtype")
+    lib = talking_attention_library()
+    _run(lib, lib.mb_talking_attention_rows(
+        _p(q), q.stride(0), _p(out), out.stride(0), _code(q.dtype), _p(k_pool), _p(v_pool), _p(block_table),
+        block_table.shape[1], _p(cu_q), _p(kv_lens), kv_lens.numel(), max_q_len, _p(talk), _p(gate),
+        gate.stride(0) if gate is not None else 0, heads, kv_heads, head_dim, value_dim, page_size, window or 0, keep_first,
+        ctypes.c_float(scale), ctypes.c_float(out_scale), _stream()))
+
+
+def gated_recurrence_library():
+    return load_library("mb_gated_recurrence", ["gated_recurrence.cu"])
+
+
+def mingru_scan(zin: torch.Tensor, xin: torch.Tensor, gin: torch.Tensor, z_bias: torch.Tensor, x_bias: torch.Tensor,
+                state: torch.Tensor, slots: torch.Tensor, cu_q: torch.Tensor, max_q_len: int, out: torch.Tensor,
+                out_scale: float = 1.0) -> None:
+    """minGRU over the new tokens of every sequence: z = sigmoid(zin + z_bias), u = xin + x_bias, candidate
+    u + 1/2 (u >= 0) or sigmoid(u); S = (1 - z) S + z candidate from the sequence's row of `state` (float32
+    [slots, width], updated in place); out = out_scale * S * silu(gin).  zin, xin, gin are column slices
+    with one row stride; arithmetic in float."""
+    _cuda(zin, xin, gin, z_bias, x_bias, state, slots, cu_q, out)
+    _int32(slots, "slots")
+    _int32(cu_q, "cu_q")
+    width = state.shape[1]
+    for name, t in (("zin", zin), ("xin", xin), ("gin", gin), ("out", out)):
+        _columns(t, name)
+        if t.shape != zin.shape or t.shape[1] != width or t.dtype != zin.dtype:
+            raise KernelError(f"mingru_scan: {name} is {tuple(t.shape)} {t.dtype}; [{zin.shape[0]}, {width}] {zin.dtype} is needed")
+    if not (zin.stride(0) == xin.stride(0) == gin.stride(0)):
+        raise KernelError("mingru_scan: zin, xin and gin must share one row stride")
+    if state.dtype != torch.float32 or not state.is_contiguous():
+        raise KernelError("mingru_scan: the state must be contiguous float32 [slots, width]")
+    for name, t in (("z_bias", z_bias), ("x_bias", x_bias)):
+        if t.dtype != torch.float32 or t.numel() != width or not t.is_contiguous():
+            raise KernelError(f"mingru_scan: {name} must be contiguous float32 of {width} elements")
+    lib = gated_recurrence_library()
+    _run(lib, lib.mb_mingru_scan(_p(zin), _p(xin), _p(gin), zin.stride(0), _code(zin.dtype), _p(z_bias), _p(x_bias), _p(state),
+                                 _p(slots), _p(cu_q), cu_q.numel() - 1, max_q_len, width, _p(out), out.stride(0),
+                                 ctypes.c_float(out_scale), _stream()))
 
 
 def _check_paged(q, out, k_pool, v_pool, block_table, cu_q, kv_lens, kv_heads, head_dim):

@@ -40,3 +40,52 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> tor
     if out_dtype == torch.float32:
         return torch.mm(a, weight.t(), out_dtype=torch.float32)
     return torch.mm(a, weight.t())
+
+
+def add_linear(x: torch.Tensor, a: torch.Tensor, weight: torch.Tensor) -> None:
+    """x += a . weight^T for the float32 residual stream x [rows, out] and weight [out, in].  Where one of
+    this package's bfloat16 products takes the sizes, the addition rides in its epilogue (the product's sums
+    stay float32 all the way into the stream); otherwise the product's float32 result is added by a kernel."""
+    if not x.is_cuda:
+        raise ops.KernelError("models_b200 runs on a CUDA device only; there is no CPU path")
+    rows = a.shape[0]
+    if weight.dtype == torch.bfloat16 and a.dtype == torch.bfloat16 and a.stride(1) == 1 and a.stride(0) % 8 == 0 \
+            and a.data_ptr() % 16 == 0:
+        if ops.skinny_pays(weight, rows):
+            ops.skinny_gemm(weight, ops.EPI_RESIDUAL, x=a, out=x)
+            return
+        if ops.gemm_tcgen05_takes(weight, ops.EPI_RESIDUAL, rows):
+            ops.tensor_core_gemm(a, weight, ops.EPI_RESIDUAL, out=x)
+            return
+    ops.residual_add(x, linear(a, weight, torch.float32))
+
+
+def stack_rows(matrices, multiple: int = 8):
+    """Matrices [n_i, k] stacked into one [sum of padded n_i, k], each padded with zero rows to a multiple of
+    `multiple` so that every part starts on a 16-byte boundary of a product's result row; returns the matrix
+    and each part's first row."""
+    parts, starts, at = [], [], 0
+    for m in matrices:
+        starts.append(at)
+        parts.append(m)
+        pad = -m.shape[0] % multiple
+        if pad:
+            parts.append(torch.zeros((pad, m.shape[1]), dtype=m.dtype, device=m.device))
+        at += m.shape[0] + pad
+    return torch.cat(parts, dim=0).contiguous(), starts
+
+
+def stack_columns(matrices, multiple: int = 8):
+    """Matrices [n, k_i] put side by side into one [n, sum of padded k_i], each padded with zero columns to a
+    multiple of `multiple`; returns the matrix, each part's first column, and whether any column is padding
+    (the activations that meet padding columns must then be finite, zeros for instance)."""
+    parts, starts, at, padded = [], [], 0, False
+    for m in matrices:
+        starts.append(at)
+        parts.append(m)
+        pad = -m.shape[1] % multiple
+        if pad:
+            parts.append(torch.zeros((m.shape[0], pad), dtype=m.dtype, device=m.device))
+            padded = True
+        at += m.shape[1] + pad
+    return torch.cat(parts, dim=1).contiguous(), starts, padded
