@@ -1,0 +1,311 @@
+// Tensor-core form of the attention of csrc/talking_attention.cu for steps that bring many tokens
+// (prompts): bfloat16 storage, m16n8k16 products, compiled for one head count and one pair of key and
+// value sizes: -DMB_HEADS=<1..16> -DMB_KEY_DIM=<multiple of 16> -DMB_VALUE_DIM=<multiple of 16>.
+//
+// A block owns 16 consecutive query tokens of one sequence with ALL their heads, one warp per head,
+// because the weights of a key are mixed across heads after the softmax: w'_h(i, j) = sum_g talk[h, g]
+// w_g(i, j) needs every head's normalised weight.  The visible keys are walked twice in chunks of 32:
+//   walk 1: S_g = Q_g K_c^T per warp, running maximum and sum of every row;
+//   walk 2: S_g again, w_g = exp(S_g - max_g) / sum_g in float, handed to the other warps through shared
+//           memory in the layout of the accumulator registers (lane-major, so nobody meets in a bank); each
+//           warp mixes its own head's weights from all heads' in float, splits them into two bfloat16
+//           numbers (w' = hi + lo, which keeps about 16 bits of the float weight) and adds
+//           hi . V_c + lo . V_c into its output accumulator.
+// Keys and values of a chunk are copied to shared memory once per block for all key/value heads.
+// Scores, weights, the mixing and every sum are float; only the operands of the products are bfloat16.
+#include "common.cuh"
+
+#include <math_constants.h>
+
+#if !defined(MB_HEADS) || !defined(MB_KEY_DIM) || !defined(MB_VALUE_DIM)
+#error "compile with -DMB_HEADS, -DMB_KEY_DIM and -DMB_VALUE_DIM"
+#endif
+
+MB_DEFINE_LAST_ERROR()
+
+namespace mb {
+
+constexpr int H = MB_HEADS, D = MB_KEY_DIM, DV = MB_VALUE_DIM;
+static_assert(H >= 1 && H <= 16, "one warp per head, at most 16");
+static_assert(D % 16 == 0 && D >= 16 && D <= 256, "key size must be a multiple of 16 in 16..256");
+static_assert(DV % 16 == 0 && DV >= 16 && DV <= 256, "value size must be a multiple of 16 in 16..256");
+constexpr int kRows = 16;                // query tokens per block
+constexpr int kKeys = 32;                // keys per chunk
+constexpr int kKRow = D * 2 + 16;        // padded shared-memory rows: ldmatrix reads without bank conflicts
+constexpr int kVRow = DV * 2 + 16;
+constexpr int kThreads = 32 * H;
+constexpr int kWeightFloats = 16 * 32;   // one head's weights of a chunk: [register][lane]
+
+using bf16 = __nv_bfloat16;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float quad_max(float v) {
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+    return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+}
+__device__ __forceinline__ float quad_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    return v + __shfl_xor_sync(0xffffffffu, v, 2);
+}
+
+// 32 positions of one page, every key/value head, into padded rows [head][32][row bytes].  Rows of positions
+// beyond `last_pos` become zeros when `zero_beyond` (values: a weight of zero must meet a finite number).
+template <int kDim, int kRowBytes>
+__device__ __forceinline__ void load_chunk(unsigned char* dst, const bf16* __restrict__ pool, size_t page, int kv_heads,
+                                           int page_size, int offset, int first_key, int last_pos, bool zero_beyond) {
+    constexpr int kPieces = kDim / 8;
+    for (int i = threadIdx.x; i < kv_heads * kKeys * kPieces; i += kThreads) {
+        const int piece = i % kPieces, row = (i / kPieces) % kKeys, head = i / (kPieces * kKeys);
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (!zero_beyond || first_key + row <= last_pos)
+            v = *reinterpret_cast<const uint4*>(pool + ((page * kv_heads + head) * page_size + offset + row) * (size_t)kDim + piece * 8);
+        *reinterpret_cast<uint4*>(dst + (size_t)(head * kKeys + row) * kRowBytes + piece * 16) = v;
+    }
+}
+
+// S[16 x 32 keys] of one warp's head: four accumulators of 8 keys.
+__device__ __forceinline__ void chunk_scores(float (&s)[4][4], uint32_t q_rows, uint32_t k_rows) {
+    const int lane = threadIdx.x & 31;
+    const int q_row = (lane & 7) + ((lane >> 3) & 1) * 8;
+    const int k_row = (lane & 7) + ((lane >> 4) & 1) * 8;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+        uint32_t a[4], b[4];
+        ldmatrix_x4(a, q_rows + q_row * kKRow + (ks * 2 + (lane >> 4)) * 16);
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {
+            ldmatrix_x4(b, k_rows + (part * 16 + k_row) * kKRow + (ks * 2 + ((lane >> 3) & 1)) * 16);
+            mma_bf16(s[2 * part], a, b[0], b[1]);
+            mma_bf16(s[2 * part + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+// grid (tiles of 16 query tokens, sequences); block 32 * H.
+__global__ void __launch_bounds__(kThreads)
+talking_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
+                            const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool, const int* __restrict__ block_table,
+                            int max_blocks, const int* __restrict__ cu_q, const int* __restrict__ kv_lens,
+                            const float* __restrict__ talk, const bf16* __restrict__ gate_in, int gate_stride, int kv_heads,
+                            int page_size, int window, int keep_first, float scale, float out_scale) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int seq = blockIdx.y;
+    const int q_begin = cu_q[seq];
+    const int q_len = cu_q[seq + 1] - q_begin;
+    const int tile = gridDim.x - 1 - blockIdx.x;  // the tiles with the most keys start first
+    const int t0 = tile * kRows;
+    if (t0 >= q_len) return;
+    const int valid = min(kRows, q_len - t0);
+    const int pos0 = kv_lens[seq] - q_len + t0, last_pos = pos0 + valid - 1;
+    const int head = threadIdx.x >> 5, lane = threadIdx.x & 31, group_id = lane >> 2, tid4 = lane & 3;
+    const int kv_head = head / (H / kv_heads);
+
+    unsigned char* q_smem = smem;                                            // [H][16][kKRow]
+    unsigned char* k_smem = q_smem + (size_t)H * kRows * kKRow;             // [kv_heads][32][kKRow]
+    unsigned char* v_smem = k_smem + (size_t)kv_heads * kKeys * kKRow;      // [kv_heads][32][kVRow]
+    float* w_smem = reinterpret_cast<float*>(v_smem + (size_t)kv_heads * kKeys * kVRow);  // [H][16][32]
+    float* talk_smem = w_smem + H * kWeightFloats;                          // [H][H]
+
+    // queries: a row beyond the step's tokens repeats the last one (it is computed and not stored)
+    for (int i = threadIdx.x; i < H * kRows * (D / 8); i += kThreads) {
+        const int piece = i % (D / 8), row = (i / (D / 8)) % kRows, h = i / ((D / 8) * kRows);
+        const int source = row < valid ? row : valid - 1;
+        *reinterpret_cast<uint4*>(q_smem + (size_t)(h * kRows + row) * kKRow + piece * 16) =
+            *reinterpret_cast<const uint4*>(q + (size_t)(q_begin + t0 + source) * q_stride + h * D + piece * 8);
+    }
+    if (talk != nullptr)
+        for (int i = threadIdx.x; i < H * H; i += kThreads) talk_smem[i] = talk[i];
+    __syncthreads();
+    float mix[H];
+#pragma unroll
+    for (int g = 0; g < H; ++g) mix[g] = talk != nullptr ? talk_smem[head * H + g] : (g == head ? 1.0f : 0.0f);
+
+    int row_pos[2], row_first[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = group_id + 8 * r;
+        row_pos[r] = pos0 + (row < valid ? row : valid - 1);
+        row_first[r] = (window > 0 && row_pos[r] - window + 1 > 0) ? row_pos[r] - window + 1 : 0;
+    }
+    const int window_first = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;  // of the tile's first row
+    const int kept_end = keep_first < window_first ? keep_first : window_first;
+    const float scale_log2 = scale * 1.4426950408889634f;
+    const int* table = block_table + (size_t)seq * max_blocks;
+    const uint32_t q_rows = smem_u32(q_smem) + head * kRows * kKRow;
+    const uint32_t k_rows = smem_u32(k_smem) + kv_head * kKeys * kKRow;
+    const uint32_t v_rows = smem_u32(v_smem) + kv_head * kKeys * kVRow;
+
+    // walk 1: maximum and sum of every row of every head
+    float run_max[2] = {-CUDART_INF_F, -CUDART_INF_F}, run_sum[2] = {0.0f, 0.0f};
+    for (int range = 0; range < 2; ++range) {
+        const int begin = range == 0 ? 0 : window_first, end = range == 0 ? kept_end : last_pos + 1;
+        for (int chunk = begin - begin % kKeys; chunk < end; chunk += kKeys) {
+            load_chunk<D, kKRow>(k_smem, k_pool, table[chunk / page_size], kv_heads, page_size, chunk % page_size, chunk, last_pos, false);
+            __syncthreads();
+            float s[4][4];
+            chunk_scores(s, q_rows, k_rows);
+            float part_max[2] = {-CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int key = chunk + nt * 8 + tid4 * 2 + (i & 1), r = i >> 1;
+                    const bool seen = key >= begin && key < end && key <= row_pos[r] && (key >= row_first[r] || key < keep_first);
+                    s[nt][i] = seen ? s[nt][i] * scale_log2 : -CUDART_INF_F;
+                    part_max[r] = fmaxf(part_max[r], s[nt][i]);
+                }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const float new_max = fmaxf(run_max[r], quad_max(part_max[r]));
+                const float safe = new_max == -CUDART_INF_F ? 0.0f : new_max;  // a row that has seen nothing yet
+                float local = 0.0f;
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) local += exp2f(s[nt][2 * r] - safe) + exp2f(s[nt][2 * r + 1] - safe);
+                run_sum[r] = run_sum[r] * exp2f(run_max[r] - safe) + local;
+                run_max[r] = new_max;
+            }
+            __syncthreads();
+        }
+    }
+    float inv_sum[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) inv_sum[r] = 1.0f / quad_sum(run_sum[r]);  // every row sees its own position
+
+    // walk 2: normalised weights, mixed across heads, applied to the values
+    float o[DV / 8][4];
+#pragma unroll
+    for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    for (int range = 0; range < 2; ++range) {
+        const int begin = range == 0 ? 0 : window_first, end = range == 0 ? kept_end : last_pos + 1;
+        for (int chunk = begin - begin % kKeys; chunk < end; chunk += kKeys) {
+            const size_t page = table[chunk / page_size];
+            load_chunk<D, kKRow>(k_smem, k_pool, page, kv_heads, page_size, chunk % page_size, chunk, last_pos, false);
+            load_chunk<DV, kVRow>(v_smem, v_pool, page, kv_heads, page_size, chunk % page_size, chunk, last_pos, true);
+            __syncthreads();
+            float s[4][4];
+            chunk_scores(s, q_rows, k_rows);
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int key = chunk + nt * 8 + tid4 * 2 + (i & 1), r = i >> 1;
+                    const bool seen = key >= begin && key < end && key <= row_pos[r] && (key >= row_first[r] || key < keep_first);
+                    s[nt][i] = seen ? exp2f(s[nt][i] * scale_log2 - run_max[r]) * inv_sum[r] : 0.0f;
+                }
+            if (talk != nullptr) {
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) w_smem[head * kWeightFloats + (nt * 4 + i) * 32 + lane] = s[nt][i];
+                __syncthreads();
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        float sum = 0.0f;
+#pragma unroll
+                        for (int g = 0; g < H; ++g) sum = fmaf(mix[g], w_smem[g * kWeightFloats + (nt * 4 + i) * 32 + lane], sum);
+                        s[nt][i] = sum;
+                    }
+            }
+#pragma unroll
+            for (int part = 0; part < 2; ++part) {
+                uint32_t hi[4], lo[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {  // accumulators (2 part + j / 2), elements 2 (j % 2) and 2 (j % 2) + 1
+                    const float a = s[2 * part + (j >> 1)][2 * (j & 1)], b = s[2 * part + (j >> 1)][2 * (j & 1) + 1];
+                    const __nv_bfloat162 top = __floats2bfloat162_rn(a, b);
+                    const __nv_bfloat162 rest = __floats2bfloat162_rn(a - __low2float(top), b - __high2float(top));
+                    hi[j] = *reinterpret_cast<const uint32_t*>(&top);
+                    lo[j] = *reinterpret_cast<const uint32_t*>(&rest);
+                }
+                const int v_row = part * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+                for (int dp = 0; dp < DV / 16; ++dp) {
+                    uint32_t b[4];
+                    ldmatrix_x4_trans(b, v_rows + v_row * kVRow + (dp * 2 + (lane >> 4)) * 16);
+                    mma_bf16(o[2 * dp], hi, b[0], b[1]);
+                    mma_bf16(o[2 * dp + 1], hi, b[2], b[3]);
+                    mma_bf16(o[2 * dp], lo, b[0], b[1]);
+                    mma_bf16(o[2 * dp + 1], lo, b[2], b[3]);
+                }
+            }
+            __syncthreads();  // the next chunk overwrites keys, values and weights
+        }
+    }
+
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = group_id + 8 * r;
+        if (row >= valid) continue;
+        float factor = out_scale;
+        if (gate_in != nullptr) {
+            const float z = __bfloat162float(gate_in[(size_t)(q_begin + t0 + row) * gate_stride + head]);
+            factor *= 1.0f / (1.0f + expf(-z));
+        }
+        bf16* dst = out + (size_t)(q_begin + t0 + row) * out_stride + (size_t)head * DV;
+#pragma unroll
+        for (int i = 0; i < DV / 8; ++i) {
+            const __nv_bfloat162 pair = __floats2bfloat162_rn(o[i][2 * r] * factor, o[i][2 * r + 1] * factor);
+            *reinterpret_cast<uint32_t*>(dst + i * 8 + tid4 * 2) = *reinterpret_cast<const uint32_t*>(&pair);
+        }
+    }
+}
+
+}  // namespace mb
+
+using namespace mb;
+
+static size_t block_bytes(int kv_heads) {
+    return (size_t)H * kRows * kKRow + (size_t)kv_heads * kKeys * (kKRow + kVRow) + sizeof(float) * ((size_t)H * kWeightFloats + H * H);
+}
+
+MB_EXPORT size_t mb_talking_attention_tc_block_bytes(int kv_heads) { return block_bytes(kv_heads); }
+
+// As mb_talking_attention_rows (csrc/talking_attention.cu), for bfloat16 and the compiled sizes.
+MB_EXPORT int mb_talking_attention_tc(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
+                                      const void* v_pool, const int* block_table, int max_blocks, const int* cu_q,
+                                      const int* kv_lens, int sequences, int max_q_len, const float* talk, const void* gate_in,
+                                      int gate_stride, int kv_heads, int page_size, int window, int keep_first, float scale,
+                                      float out_scale, cudaStream_t stream) {
+    if (sequences <= 0 || max_q_len <= 0) return 0;
+    if (kv_heads <= 0 || H % kv_heads) return fail("talking_attention_tc: %d heads are no multiple of %d kv heads", H, kv_heads);
+    if (page_size <= 0 || page_size % kKeys) return fail("talking_attention_tc: page_size %d must be a multiple of %d", page_size, kKeys);
+    if (window < 0 || keep_first < 0) return fail("talking_attention_tc: window and keep_first must not be negative");
+    if (q_stride % 8 || out_stride % 2 || ((uintptr_t)q & 15) || ((uintptr_t)out & 3) || ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15))
+        return fail("talking_attention_tc: q rows must start on 16 bytes, out rows on 4, the pools on 16");
+    if (sequences > 65535) return fail("talking_attention_tc: %d sequences exceed the grid limit 65535", sequences);
+    const size_t smem = block_bytes(kv_heads);
+    if (smem > 227 * 1024) return fail("talking_attention_tc: a block would need %zu bytes of shared memory", smem);
+    static bool configured[64] = {false};
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device < 64 && !configured[device]) {
+        cudaError_t status = cudaFuncSetAttribute(talking_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (status != cudaSuccess) return fail("talking_attention_tc: cannot reserve shared memory: %s", cudaGetErrorString(status));
+        configured[device] = true;
+    }
+    const dim3 grid((max_q_len + kRows - 1) / kRows, sequences);
+    talking_attention_tc_kernel<<<grid, kThreads, smem, stream>>>(
+        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table, max_blocks, cu_q,
+        kv_lens, talk, (const bf16*)gate_in, gate_stride, kv_heads, page_size, window, keep_first, scale, out_scale);
+    return check_launch("talking_attention_tc");
+}

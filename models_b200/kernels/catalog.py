@@ -30,6 +30,10 @@ LIBRARIES = [
     ("mb_decode_step", ["decode_step.cu"], {"MB_HEAD_DIM": 128}),
     ("mb_prefill_attention_tcgen05", ["prefill_attention_tcgen05.cu"], {"MB_HEAD_DIM": 64}),
     ("mb_prefill_attention_tcgen05", ["prefill_attention_tcgen05.cu"], {"MB_HEAD_DIM": 128}),
+    # the tensor-core attention with weights mixed across heads is compiled per (heads, key size, value size);
+    # these are the sizes of the benchmark's models of that design
+    ("mb_talking_attention_tc", ["talking_attention_tc.cu"], {"MB_HEADS": 8, "MB_KEY_DIM": 64, "MB_VALUE_DIM": 128}),
+    ("mb_talking_attention_tc", ["talking_attention_tc.cu"], {"MB_HEADS": 16, "MB_KEY_DIM": 64, "MB_VALUE_DIM": 128}),
 ]
 
 

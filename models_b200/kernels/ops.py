@@ -368,14 +368,43 @@ def rotate_store(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, positions: t
                                   head_dim, value_dim, rotary_dim, page_size, _stream()))
 
 
+def talking_attention_tc_library(heads: int, head_dim: int, value_dim: int):
+    """The tensor-core form, compiled for this head count and these key and value sizes at first use."""
+    return load_library("mb_talking_attention_tc", ["talking_attention_tc.cu"],
+                        {"MB_HEADS": int(heads), "MB_KEY_DIM": int(head_dim), "MB_VALUE_DIM": int(value_dim)})
+
+
+TALKING_TC_MIN_ROWS = 8  # steps that bring fewer tokens to every sequence go to the kernel with a block per token
+
+
+def talking_attention_tc_takes(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, heads: int,
+                               kv_heads: int, head_dim: int, value_dim: int, max_q_len: int) -> bool:
+    """bfloat16; one warp per head, so at most 16 heads; key and value sizes multiples of 16, with values no wider
+    than the registers of a block of that many warps hold as an accumulator; 16-byte query rows; and a block's
+    shared memory (queries of 16 tokens, a chunk of keys and values of every key/value head, the heads' weights)."""
+    if q.dtype != torch.bfloat16 or max_q_len < TALKING_TC_MIN_ROWS or not 1 <= heads <= 16:
+        return False
+    if head_dim % 16 or value_dim % 16 or not 16 <= head_dim <= 256 or not 16 <= value_dim <= (256 if heads <= 8 else 128):
+        return False
+    if q.stride(0) % 8 or out.stride(0) % 2 or q.data_ptr() % 16 or out.data_ptr() % 4 or k_pool.data_ptr() % 16 or v_pool.data_ptr() % 16:
+        return False
+    block = (heads * 16 * (2 * head_dim + 16) + kv_heads * 32 * (2 * head_dim + 2 * value_dim + 32) + 4 * (heads * 512 + heads * heads))
+    return block <= 227 * 1024
+
+
 def talking_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                       block_table: torch.Tensor, cu_q: torch.Tensor, kv_lens: torch.Tensor, max_q_len: int, heads: int,
                       kv_heads: int, head_dim: int, value_dim: int, window: Optional[int], keep_first: int, scale: float,
-                      talk: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, out_scale: float = 1.0) -> None:
+                      talk: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, out_scale: float = 1.0,
+                      kernel: Optional[str] = None) -> None:
     """Causal attention over the paged cache with softmax weights mixed across heads by `talk` (float32
     [heads, heads]; None: not mixed), a window that also keeps the first `keep_first` positions, value heads
     of `value_dim`, and an output gate: out_h = out_scale * sigmoid(gate[:, h]) * sum_j w'_h(j) v(j).
-    q [T, heads*head_dim], out [T, heads*value_dim], gate [T, heads] (or None) may be column slices."""
+    q [T, heads*head_dim], out [T, heads*value_dim], gate [T, heads] (or None) may be column slices.
+    `kernel`: None picks the tensor-core form where it applies (bfloat16 steps of many tokens), else the
+    form with a block per token; "tc" or "rows" asks for one of them."""
+    if kernel not in (None, "tc", "rows"):
+        raise KernelError(f"talking_attention: unknown kernel {kernel!r}")
     _cuda(q, out, k_pool, v_pool, block_table, cu_q, kv_lens, talk, gate)
     _int32(block_table, "block_table")
     _int32(cu_q, "cu_q")
@@ -397,6 +426,16 @@ def talking_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, 
         _columns(gate, "gate")
         if gate.dtype != q.dtype or tuple(gate.shape) != (q.shape[0], heads):
             raise KernelError(f"gate must be [{q.shape[0]}, {heads}] of q's dtype")
+    if kernel == "tc" or (kernel is None and talking_attention_tc_takes(q, out, k_pool, v_pool, heads, kv_heads, head_dim, value_dim,
+                                                                      max_q_len)):
+        if q.dtype != torch.bfloat16:
+            raise KernelError("the tensor-core form takes bfloat16")
+        lib = talking_attention_tc_library(heads, head_dim, value_dim)
+        _run(lib, lib.mb_talking_attention_tc(
+            _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pool), _p(v_pool), _p(block_table), block_table.shape[1], _p(cu_q),
+            _p(kv_lens), kv_lens.numel(), max_q_len, _p(talk), _p(gate), gate.stride(0) if gate is not None else 0, kv_heads,
+            page_size, window or 0, keep_first, ctypes.c_float(scale), ctypes.c_float(out_scale), _stream()))
+        return
     lib = talking_attention_library()
     _run(lib, lib.mb_talking_attention_rows(
         _p(q), q.stride(0), _p(out), out.stride(0), _code(q.dtype), _p(k_pool), _p(v_pool), _p(block_table),

@@ -52,7 +52,7 @@ def _paged(k, v, page_size, device, dtype, shuffle_seed=0):
     return k_pool, v_pool, order.to(torch.int32)[None, :].contiguous().to(device), mapping, positions.to(device)
 
 
-def _attend(q, k, v, talk, gate, scale, window, keep_first, dtype, device, page_size=64, q_len=None, out_scale=1.0):
+def _attend(q, k, v, talk, gate, scale, window, keep_first, dtype, device, page_size=64, q_len=None, out_scale=1.0, kernel=None):
     """The kernel's result for the last `q_len` tokens (all by default) of one sequence, as float64 [q_len, H, Dv]."""
     from models_b200.kernels import ops
 
@@ -70,7 +70,7 @@ def _attend(q, k, v, talk, gate, scale, window, keep_first, dtype, device, page_
     gate_d = gate[T - q_len:].to(dtype).to(device).contiguous() if gate is not None else None
     talk_d = talk.float().to(device).contiguous() if talk is not None else None
     ops.talking_attention(rows[:, :a], out, k_pool, v_pool, table, cu_q, kv_lens, q_len, H, G, D, Dv, window, keep_first, scale,
-                          talk_d, gate_d, out_scale)
+                          talk_d, gate_d, out_scale, kernel)
     return out.double().cpu().reshape(q_len, H, Dv)
 
 
@@ -99,7 +99,7 @@ def test_one_key_decides_the_attention(cuda_device, tokens, window, keep_first, 
     """The last query's heads all point at one key, whose value is far from the others'.  Whether that key is
     visible changes the result grossly; every row is compared with the plain attention."""
     g = torch.Generator().manual_seed(tokens + target)
-    H, G, D, Dv = 4, 2, 16, 8
+    H, G, D, Dv = 4, 2, 16, 16
     q = torch.randn((tokens, H, D), generator=g, dtype=F)
     k = torch.randn((tokens, G, D), generator=g, dtype=F)
     v = torch.randn((tokens, G, Dv), generator=g, dtype=F)
@@ -114,15 +114,19 @@ def test_one_key_decides_the_attention(cuda_device, tokens, window, keep_first, 
     expected = pk.talking_attention(q, k, v, talk.float().to(F), gate, 0.5, window, keep_first)
     seen = pk.visible(tokens, window, keep_first)[-1, target].item()
     assert (expected[-1].abs().max() > 10.0) == seen  # the case shows what it is meant to show
-    got = _attend(q, k, v, talk, gate, 0.5, window, keep_first, dtype, cuda_device)
     tol = 1e-5 if dtype == torch.float32 else 1e-2
-    assert scaled_error(got, expected) < tol
+    for kernel in ("rows", "tc") if dtype == torch.bfloat16 else ("rows",):  # a block per token; the tensor-core tiles
+        got = _attend(q, k, v, talk, gate, 0.5, window, keep_first, dtype, cuda_device, kernel=kernel)
+        assert scaled_error(got, expected) < tol, kernel
+        part = _attend(q, k, v, talk, gate, 0.5, window, keep_first, dtype, cuda_device, q_len=37, kernel=kernel)  # a portion
+        assert scaled_error(part, expected[-37:]) < tol, kernel
     last = _attend(q, k, v, talk, gate, 0.5, window, keep_first, dtype, cuda_device, q_len=1)  # as a decode step sees it
     assert scaled_error(last[0], expected[-1]) < tol
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,kv_heads,dim,vdim,page", [(1, 1, 8, 8, 32), (6, 2, 20, 12, 64), (3, 3, 40, 72, 128), (16, 4, 64, 128, 64)])
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim,page", [(1, 1, 8, 8, 32), (6, 2, 20, 12, 64), (3, 3, 40, 72, 128), (16, 4, 64, 128, 64),
+                                                          (1, 1, 16, 16, 32), (6, 3, 96, 160, 64), (8, 8, 32, 48, 128), (12, 2, 48, 64, 64)])
 def test_attention_sizes_mixing_gate_and_scale(cuda_device, heads, kv_heads, dim, vdim, page, dtype):
     g = torch.Generator().manual_seed(heads * 100 + dim)
     T = 150
@@ -135,9 +139,11 @@ def test_attention_sizes_mixing_gate_and_scale(cuda_device, heads, kv_heads, dim
     for use_talk, use_gate, out_scale in ((True, True, 1.7), (False, True, 1.0), (True, False, 0.5)):
         expected = out_scale * pk.talking_attention(q, k, v, talk.float().to(F) if use_talk else None, gate if use_gate else None,
                                                     0.3, 37, 5)
-        got = _attend(q, k, v, talk if use_talk else None, gate if use_gate else None, 0.3, 37, 5, dtype, cuda_device,
-                      page_size=page, out_scale=out_scale)
-        assert scaled_error(got, expected) < tol, (use_talk, use_gate)
+        takes_tc = dtype == torch.bfloat16 and dim % 16 == 0 and vdim % 16 == 0
+        for kernel in ("rows", "tc") if takes_tc else ("rows",):
+            got = _attend(q, k, v, talk if use_talk else None, gate if use_gate else None, 0.3, 37, 5, dtype, cuda_device,
+                          page_size=page, out_scale=out_scale, kernel=kernel)
+            assert scaled_error(got, expected) < tol, (use_talk, use_gate, kernel)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
