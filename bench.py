@@ -311,6 +311,172 @@ def device_prefill(model, tokens, repeats=5):
     return statistics.median(times[warm:])
 
 
+# ------------------------------------------------------------------------------------------------
+# --design kabanex: the Kabanex decoder beside a Llama of equal size (same width, layers, heads, key/value
+# heads, window, vocabulary, and a feed-forward width that makes the layers' parameters equal), random
+# weights, prefill and decode through the engine, and the design's own kernels alone beside their Llama
+# counterparts.  The default run of this file does not come here.
+
+DESIGN_SIZES = {
+    # width, layers, heads, kv_heads, key size, value size, recurrent width, ff, window, kept first positions
+    "s": dict(width=1024, layers=8, heads=8, kv_heads=2, dim=64, vdim=128, recurrent=1024, ff=2048, window=512, keep_first=4),
+    "m": dict(width=2048, layers=16, heads=16, kv_heads=4, dim=64, vdim=128, recurrent=2048, ff=4096, window=1024, keep_first=4),
+}
+DESIGN_VOCAB = 32768
+
+
+def kabanex_config(z):
+    layer = {"type": "parallel",
+             "mixer": {"left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"],
+                                "scale": z["dim"] ** -0.5, "rot": {"dims": z["dim"] // 2, "base": 500000.0},
+                                "mask": {"size": z["window"], "keep_first": z["keep_first"]}},
+                       "right": {"width": z["recurrent"]}, "left_scale": 1.0, "right_scale": 1.0},
+             "mlp": {"kind": "dense", "ff": z["ff"]}}
+    return {"architecture": "Kabanex", "vocab": DESIGN_VOCAB, "width": z["width"], "norm": {"eps": 1e-6},
+            "layers": [layer] * z["layers"]}
+
+
+def kabanex_layer_params(z):
+    w, h, g = z["width"], z["heads"], z["kv_heads"]
+    first = h * z["dim"] + g * z["dim"] + g * z["vdim"] + h + 3 * z["recurrent"] + z["ff"]
+    return w * first + w * (h * z["vdim"] + z["recurrent"] + z["ff"])
+
+
+def llama_like(z):
+    """A Llama with the same width, layers, heads, key/value heads and window, heads of 128 (queries and values as
+    wide as the design's values), and the feed-forward width that makes a layer's parameters equal (a multiple of 256)."""
+    w, h, g, hd = z["width"], z["heads"], z["kv_heads"], 128
+    attention = w * (h * hd + 2 * g * hd) + h * hd * w
+    inter = max(256, round((kabanex_layer_params(z) - attention) / (3 * w) / 256) * 256)
+    return dict(LLAMA_3_2_1B, num_hidden_layers=z["layers"], hidden_size=w, num_attention_heads=h, num_key_value_heads=g,
+                head_dim=hd, intermediate_size=inter, vocab_size=DESIGN_VOCAB, sliding_window=z["window"], rope_scaling=None,
+                tie_word_embeddings=False, max_position_embeddings=8192)
+
+
+def time_kernel(call, repeats=7):
+    """Median device time of `call()` in microseconds, L2 flushed before every run."""
+    import torch
+
+    flush = torch.empty(64 * 1024 * 1024, dtype=torch.float32, device="cuda")  # 256 MB > 126 MB of L2
+    for _ in range(3):
+        call()
+    times = []
+    for _ in range(repeats):
+        flush.zero_()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        call()
+        end.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(end) * 1e3)
+    return statistics.median(times)
+
+
+def design_kernels(z, peak, prompt=2048, batch=8, context=1536):
+    """The design's kernels alone beside the like Llama kernels at equal sizes: attention over a prompt and in a
+    decode step, the recurrence, the norm; each with its fraction of the measured peak that bounds it."""
+    import torch
+
+    from models_b200.kernels import ops
+
+    dev, bf = "cuda", torch.bfloat16
+    H, G, D, DV, R, W, window, keep = (z[k] for k in ("heads", "kv_heads", "dim", "vdim", "recurrent", "width", "window", "keep_first"))
+    page = 64
+    out = {}
+
+    def paged(sequences, length, key, value):
+        pages = sequences * (-(-length // page))
+        k_pool = torch.randn((pages + 1, G, page, key), device=dev).to(bf)
+        v_pool = torch.randn((pages + 1, G, page, value), device=dev).to(bf)
+        table = (torch.arange(pages, dtype=torch.int32, device=dev) + 1).reshape(sequences, -1).contiguous()
+        return k_pool, v_pool, table
+
+    def seen(length, q_len):  # (query, key) pairs a step of q_len tokens ending at `length` looks at
+        return sum(min(p + 1, window) + min(keep, max(0, p + 1 - window)) for p in range(length - q_len, length))
+
+    # a prompt of `prompt` tokens, one sequence
+    cu, kv = torch.tensor([0, prompt], dtype=torch.int32, device=dev), torch.tensor([prompt], dtype=torch.int32, device=dev)
+    pairs = seen(prompt, prompt)
+    k_pool, v_pool, table = paged(1, prompt, D, DV)
+    q, o = torch.randn((prompt, H * D), device=dev).to(bf), torch.empty((prompt, H * DV), dtype=bf, device=dev)
+    talk, gate = torch.randn((H, H), device=dev), torch.randn((prompt, H), device=dev).to(bf)
+    us = time_kernel(lambda: ops.talking_attention(q, o, k_pool, v_pool, table, cu, kv, prompt, H, G, D, DV, window, keep, D ** -0.5, talk, gate))
+    flops = pairs * H * (2 * D + 2 * DV + 2 * H)  # scores once, values once, the mixing; what the mechanism asks for
+    out["prompt_attention_kabanex"] = {"us": us, "tflops": flops / us / 1e6, "frac_of_bf16_peak": flops / us / 1e6 / peak["bf16_tflops"]}
+    hd = 128
+    k2, v2, _ = paged(1, prompt, hd, hd)
+    q2, o2 = torch.randn((prompt, H * hd), device=dev).to(bf), torch.empty((prompt, H * hd), dtype=bf, device=dev)
+    us = time_kernel(lambda: ops.prefill_attention(q2, o2, k2, v2, table, cu, kv, prompt, H, G, hd, window, hd ** -0.5))
+    flops = pairs * H * 4 * hd
+    out["prompt_attention_llama"] = {"us": us, "tflops": flops / us / 1e6, "frac_of_bf16_peak": flops / us / 1e6 / peak["bf16_tflops"]}
+
+    # a decode step of `batch` sequences that hold `context` positions
+    cu = torch.arange(batch + 1, dtype=torch.int32, device=dev)
+    kv = torch.full((batch,), context, dtype=torch.int32, device=dev)
+    pairs = batch * seen(context, 1)
+    k_pool, v_pool, table = paged(batch, context, D, DV)
+    q, o = torch.randn((batch, H * D), device=dev).to(bf), torch.empty((batch, H * DV), dtype=bf, device=dev)
+    gate = torch.randn((batch, H), device=dev).to(bf)
+    us = time_kernel(lambda: ops.talking_attention(q, o, k_pool, v_pool, table, cu, kv, 1, H, G, D, DV, window, keep, D ** -0.5, talk, gate))
+    moved = pairs * G * (D + DV) * 2
+    out["decode_attention_kabanex"] = {"us": us, "gbs": moved / us / 1e3, "frac_of_hbm_peak": moved / us / 1e3 / peak["hbm_gbs"]}
+    k2, v2, _ = paged(batch, context, hd, hd)
+    q2, o2 = torch.randn((batch, H * hd), device=dev).to(bf), torch.empty((batch, H * hd), dtype=bf, device=dev)
+    splits = ops.decode_splits(batch, H, G, hd, context, window, ops.multiprocessors(torch.device(dev)))
+    us = time_kernel(lambda: ops.decode_attention(q2, o2, k2, v2, table, cu, kv, H, G, hd, window, hd ** -0.5, splits))
+    moved = pairs * G * 2 * hd * 2
+    out["decode_attention_llama"] = {"us": us, "gbs": moved / us / 1e3, "frac_of_hbm_peak": moved / us / 1e3 / peak["hbm_gbs"]}
+
+    # the recurrence over a prompt and in a decode step; the layer norm beside the RMS norm
+    state = torch.zeros((batch + 1, R), dtype=torch.float32, device=dev)
+    zb, xb = torch.zeros(R, device=dev), torch.zeros(R, device=dev)
+    for name, rows, cu_q, longest in (("prompt", prompt, [0, prompt], prompt), ("decode", batch, list(range(batch + 1)), 1)):
+        proj, y = torch.randn((rows, 3 * R), device=dev).to(bf), torch.empty((rows, R), dtype=bf, device=dev)
+        cu_t = torch.tensor(cu_q, dtype=torch.int32, device=dev)
+        slots = torch.arange(len(cu_q) - 1, dtype=torch.int32, device=dev)
+        us = time_kernel(lambda: ops.mingru_scan(proj[:, :R], proj[:, R:2 * R], proj[:, 2 * R:], zb, xb, state, slots, cu_t, longest, y))
+        moved = rows * R * 2 * 4 + (len(cu_q) - 1) * R * 8
+        out[f"{name}_recurrence"] = {"us": us, "gbs": moved / us / 1e3, "frac_of_hbm_peak": moved / us / 1e3 / peak["hbm_gbs"]}
+    x = torch.randn((prompt, W), device=dev)
+    gain, bias = torch.ones(W, device=dev), torch.zeros(W, device=dev)
+    moved = prompt * W * 6
+    us = time_kernel(lambda: ops.layernorm(x, gain, bias, 1e-6, bf))
+    out["prompt_layernorm"] = {"us": us, "gbs": moved / us / 1e3, "frac_of_hbm_peak": moved / us / 1e3 / peak["hbm_gbs"]}
+    us = time_kernel(lambda: ops.add_rmsnorm(x, None, gain, 1e-6, bf))
+    out["prompt_rmsnorm_llama"] = {"us": us, "gbs": moved / us / 1e3, "frac_of_hbm_peak": moved / us / 1e3 / peak["hbm_gbs"]}
+    return out
+
+
+def design_run(args) -> int:
+    import torch
+
+    peak = peaks()
+    batch, prompt, prefill_tokens, steps, warmup = 8, 512, 2048, args.steps or 64, max(args.warmup, 3)
+    sizes = {}
+    for name, z in DESIGN_SIZES.items():
+        entry = {"sizes": z, "layer_params": kabanex_layer_params(z)}
+        for arch, config in (("kabanex", kabanex_config(z)), ("llama", llama_like(z))):
+            model = make_model(config, batch, prefill_tokens + 64)
+            ms = device_prefill(model, prefill_tokens)
+            run = device_decode(model, batch, steps, warmup, prompt=prompt)
+            entry[arch] = {"prefill_tokens_per_s": prefill_tokens / (ms / 1e3), "prefill_ms": ms,
+                           "decode_tokens_per_s": run["tokens_per_second"], "decode_ms_per_step": run["ms_per_step"],
+                           "launches_per_step": run["launches"] / steps, "kernels": run["kernels"]}
+            if arch == "llama":
+                entry[arch]["intermediate_size"] = config["intermediate_size"]
+            model.close()
+            del model
+            torch.cuda.empty_cache()
+        entry["kernels_alone"] = design_kernels(z, peak)
+        sizes[name] = entry
+    print(json.dumps({"design": "Kabanex", "beside": "LlamaForCausalLM of equal size", "dtype": "bf16", "gpu": torch.cuda.get_device_name(0),
+                      "data": "synthetic: seeded uniform-random token ids, random weights N(0, 0.02)",
+                      "workload": {"prefill_tokens": prefill_tokens, "decode_batch": batch, "decode_prompt": prompt, "decode_steps": steps,
+                                   "warmup": warmup, "vocab": DESIGN_VOCAB},
+                      "peaks": peak, "sizes": sizes}))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -326,7 +492,14 @@ def main() -> int:
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 decode points and the prefill")
     parser.add_argument("--only-prefill", action="store_true",
                         help="run the workload's prefill alone and print its figures (for profiling)")
+    parser.add_argument("--design", default=None, choices=["kabanex"],
+                        help="instead of the default run: this design beside a Llama of equal size (prefill, decode, its kernels alone)")
     args = parser.parse_args()
+    if args.design and args.impl == "ours":
+        if args.gpus != 1:
+            print(f"bench.py measures one GPU: --gpus {args.gpus} is not built")
+            return 2
+        return design_run(args)
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": (

@@ -332,15 +332,30 @@ inline int grid_for(size_t total, int block) {
     return (int)(blocks > 148 * 16 ? 148 * 16 : (blocks ? blocks : 1));
 }
 
-// One block per output row.  Two walks: the mean, then the mean of the squared deviations from it.
+// One block per output row.  Two walks: the mean, then the mean of the squared deviations from it.  The row is
+// read from memory once and kept in shared memory (`cached`: it fits), else read again for every walk.
 template <typename Out>
 __global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ weight, const float* __restrict__ bias,
-                                 Out* __restrict__ out, const int* __restrict__ rows, int width, float eps) {
+                                 Out* __restrict__ out, const int* __restrict__ rows, int width, float eps, int cached) {
     __shared__ float scratch[32];
+    extern __shared__ float kept[];
     const int source = rows != nullptr ? rows[blockIdx.x] : blockIdx.x;
     const float* row = x + (size_t)source * width;
     float sum = 0.0f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) sum += row[i];
+    if (cached) {
+        if ((width & 3) == 0) {
+            for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+                const float4 v = *reinterpret_cast<const float4*>(row + i);
+                *reinterpret_cast<float4*>(kept + i) = v;
+                sum += (v.x + v.y) + (v.z + v.w);
+            }
+        } else {
+            for (int i = threadIdx.x; i < width; i += blockDim.x) sum += (kept[i] = row[i]);
+        }
+        row = kept;  // (every thread reads back only after the barrier inside block_sum)
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) sum += row[i];
+    }
     const float mean = block_sum(sum, scratch) / (float)width;
     float squares = 0.0f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
@@ -487,10 +502,12 @@ MB_EXPORT int mb_layernorm(const float* x, const float* weight, const float* bia
                            int out_rows, int width, float eps, cudaStream_t stream) {
     if (out_rows <= 0 || width <= 0) return 0;
     const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
+    const int cached = width <= 10240 ? 1 : 0;  // 40 KB of a block's shared memory
+    const size_t smem = cached ? sizeof(float) * (size_t)width : 0;
     if (out_dtype == MB_F32)
-        layernorm_kernel<float><<<out_rows, threads, 0, stream>>>(x, weight, bias, (float*)out, rows, width, eps);
+        layernorm_kernel<float><<<out_rows, threads, smem, stream>>>(x, weight, bias, (float*)out, rows, width, eps, cached);
     else if (out_dtype == MB_BF16)
-        layernorm_kernel<__nv_bfloat16><<<out_rows, threads, 0, stream>>>(x, weight, bias, (__nv_bfloat16*)out, rows, width, eps);
+        layernorm_kernel<__nv_bfloat16><<<out_rows, threads, smem, stream>>>(x, weight, bias, (__nv_bfloat16*)out, rows, width, eps, cached);
     else
         return fail("layernorm: unknown dtype code %d", out_dtype);
     return check_launch("layernorm");

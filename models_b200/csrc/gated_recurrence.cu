@@ -42,14 +42,33 @@ __global__ void mingru_scan_kernel(const T* __restrict__ zin, const T* __restric
     const int t0 = min(chunk * per, count), t1 = min(t0 + per, count);
     const float bz = live ? z_bias[channel] : 0.0f, bx = live ? x_bias[channel] : 0.0f;
 
+    // Loads do not depend on the recurrence: four tokens' inputs are asked for before the first is used.
+    constexpr int kAhead = 4;
     if (chunks > 1) {
         float a = 1.0f, b = 0.0f;
         if (live) {
-            for (int t = t0; t < t1; ++t) {
+            int t = t0;
+            for (; t + kAhead <= t1; t += kAhead) {
+                float zr[kAhead], xr[kAhead];
+#pragma unroll
+                for (int u = 0; u < kAhead; ++u) {
+                    const size_t at = (size_t)(first + t + u) * in_stride + channel;
+                    zr[u] = Num<T>::load(zin + at);
+                    xr[u] = Num<T>::load(xin + at);
+                }
+#pragma unroll
+                for (int u = 0; u < kAhead; ++u) {
+                    const float z = sigmoid(zr[u] + bz), x = xr[u] + bx;
+                    const float c = x >= 0.0f ? x + 0.5f : sigmoid(x);
+                    a *= 1.0f - z;
+                    b = (1.0f - z) * b + z * c;
+                }
+            }
+            for (; t < t1; ++t) {
                 const size_t at = (size_t)(first + t) * in_stride + channel;
                 const float z = sigmoid(Num<T>::load(zin + at) + bz);
-                const float u = Num<T>::load(xin + at) + bx;
-                const float c = u >= 0.0f ? u + 0.5f : sigmoid(u);
+                const float x = Num<T>::load(xin + at) + bx;
+                const float c = x >= 0.0f ? x + 0.5f : sigmoid(x);
                 a *= 1.0f - z;
                 b = (1.0f - z) * b + z * c;
             }
@@ -62,11 +81,29 @@ __global__ void mingru_scan_kernel(const T* __restrict__ zin, const T* __restric
     float* stored = state + (size_t)slots[seq] * width + channel;
     float s = *stored;
     for (int before = 0; before < chunk; ++before) s = a_of[before][threadIdx.x] * s + b_of[before][threadIdx.x];
-    for (int t = t0; t < t1; ++t) {
+    int t = t0;
+    for (; t + kAhead <= t1; t += kAhead) {
+        float zr[kAhead], xr[kAhead], gr[kAhead];
+#pragma unroll
+        for (int u = 0; u < kAhead; ++u) {
+            const size_t at = (size_t)(first + t + u) * in_stride + channel;
+            zr[u] = Num<T>::load(zin + at);
+            xr[u] = Num<T>::load(xin + at);
+            gr[u] = Num<T>::load(gin + at);
+        }
+#pragma unroll
+        for (int u = 0; u < kAhead; ++u) {
+            const float z = sigmoid(zr[u] + bz), x = xr[u] + bx;
+            const float c = x >= 0.0f ? x + 0.5f : sigmoid(x);
+            s = (1.0f - z) * s + z * c;
+            Num<T>::store(out + (size_t)(first + t + u) * out_stride + channel, out_scale * s * (gr[u] * sigmoid(gr[u])));
+        }
+    }
+    for (; t < t1; ++t) {
         const size_t at = (size_t)(first + t) * in_stride + channel;
         const float z = sigmoid(Num<T>::load(zin + at) + bz);
-        const float u = Num<T>::load(xin + at) + bx;
-        const float c = u >= 0.0f ? u + 0.5f : sigmoid(u);
+        const float x = Num<T>::load(xin + at) + bx;
+        const float c = x >= 0.0f ? x + 0.5f : sigmoid(x);
         s = (1.0f - z) * s + z * c;
         const float g = Num<T>::load(gin + at);
         Num<T>::store(out + (size_t)(first + t) * out_stride + channel, out_scale * s * (g * sigmoid(g)));

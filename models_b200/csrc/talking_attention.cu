@@ -226,6 +226,165 @@ __global__ void __launch_bounds__(kMaxThreads) talking_attention_rows_kernel(
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Decoding: one query token per sequence.  A block per token cannot keep a GPU busy with a handful of
+// sequences, so the visible keys are cut into their chunks of 32 and every chunk gets a block, in two kernels:
+//   scores: a block computes every head's scaled scores of its chunk (scratch [sequence][head][chunk][32]) and
+//           the chunk's maximum and sum of exponentials per head (scratch [sequence][head][chunk][2]);
+//   values: a block first folds all chunks' maxima and sums into every head's maximum and sum (in chunk order),
+//           then normalises its own chunk's scores, mixes them across heads, applies them to its chunk of the
+//           values, and writes its partial result (scratch [sequence][chunk][heads * value_dim]); the block
+//           that finishes last (a ticket per sequence) adds the partial results in chunk order, applies gate
+//           and scale and stores the token's result, and puts the ticket back to zero.
+// The chunks of a sequence: those of the kept first positions [0, kept_end), then those of the window.
+
+struct DecodeChunks {
+    int pos, window_first, kept_end, kept_chunks, total;
+    __device__ __forceinline__ DecodeChunks(int kv_len, int window, int keep_first) {
+        pos = kv_len - 1;
+        window_first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        kept_end = keep_first < window_first ? keep_first : window_first;
+        kept_chunks = (kept_end + kChunk - 1) / kChunk;
+        total = kept_chunks + pos / kChunk - window_first / kChunk + 1;
+    }
+    // first position of chunk `index`, and the range of visible positions it is walked for
+    __device__ __forceinline__ void chunk(int index, int& first, int& begin, int& end) const {
+        if (index < kept_chunks) {
+            first = index * kChunk;
+            begin = 0;
+            end = kept_end;
+        } else {
+            first = (window_first / kChunk + index - kept_chunks) * kChunk;
+            begin = window_first;
+            end = pos + 1;
+        }
+    }
+};
+
+// grid (most chunks of any sequence, sequences); block 128.
+template <typename T>
+__global__ void __launch_bounds__(128) talking_decode_scores_kernel(
+    const T* __restrict__ q, int q_stride, const T* __restrict__ k_pool, const int* __restrict__ block_table, int max_blocks,
+    const int* __restrict__ cu_q, const int* __restrict__ kv_lens, float* __restrict__ scores, float* __restrict__ stats,
+    int max_chunks, int heads, int kv_heads, int head_dim, int page_size, int window, int keep_first, float scale) {
+    extern __shared__ float q_shared[];  // heads * head_dim
+    const int seq = blockIdx.y, index = blockIdx.x;
+    const DecodeChunks chunks(kv_lens[seq], window, keep_first);
+    if (index >= chunks.total) return;
+    int first, begin, end;
+    chunks.chunk(index, first, begin, end);
+    const T* q_row = q + (size_t)cu_q[seq] * q_stride;
+    for (int i = threadIdx.x; i < heads * head_dim; i += blockDim.x) q_shared[i] = Num<T>::load(q_row + i);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int group = heads / kv_heads;
+    const bool vector_ok = (head_dim % 8) == 0;
+    const size_t page = block_table[(size_t)seq * max_blocks + first / page_size];
+    const int p = first + lane;
+    const bool seen = p >= begin && p < end;
+    for (int head = warp; head < heads; head += warps) {
+        const size_t row = (page * kv_heads + head / group) * page_size + (first % page_size) + lane;
+        float score = -CUDART_INF_F;
+        if (seen) score = dot_row<T>(q_shared + head * head_dim, k_pool + row * head_dim, head_dim, vector_ok) * scale;
+        const float top = warp_max(score);  // finite: a chunk that is walked holds a visible key
+        const float sum = warp_sum(expf(score - top));
+        const size_t at = ((size_t)seq * heads + head) * max_chunks + index;
+        scores[at * kChunk + lane] = score;
+        if (lane == 0) {
+            stats[at * 2] = top;
+            stats[at * 2 + 1] = sum;
+        }
+    }
+}
+
+// grid (most chunks of any sequence, sequences); block: as for the kernel with a block per token.
+// shared: weights [heads][32], mixed [heads][32], maxima [heads], sums [heads], talk [heads^2].
+template <typename T>
+__global__ void __launch_bounds__(kMaxThreads) talking_decode_values_kernel(
+    T* __restrict__ out, int out_stride, const T* __restrict__ v_pool, const int* __restrict__ block_table, int max_blocks,
+    const int* __restrict__ cu_q, const int* __restrict__ kv_lens, const float* __restrict__ scores, const float* __restrict__ stats,
+    float* __restrict__ partial, int* __restrict__ tickets, int max_chunks, const float* __restrict__ talk,
+    const T* __restrict__ gate_in, int gate_stride, int heads, int kv_heads, int value_dim, int page_size, int window,
+    int keep_first, float out_scale) {
+    extern __shared__ float shared[];
+    __shared__ int last_block;
+    const int seq = blockIdx.y, index = blockIdx.x;
+    const DecodeChunks chunks(kv_lens[seq], window, keep_first);
+    if (index >= chunks.total) return;
+    int first, begin, end;
+    chunks.chunk(index, first, begin, end);
+    float* weights = shared;
+    float* mixed = weights + heads * kChunk;
+    float* maxima = mixed + heads * kChunk;
+    float* sums = maxima + heads;
+    float* talk_shared = sums + heads;
+    const int group = heads / kv_heads;
+    const int outputs = heads * value_dim;
+
+    for (int head = threadIdx.x; head < heads; head += blockDim.x) {
+        const float* of_head = stats + ((size_t)seq * heads + head) * max_chunks * 2;
+        float top = -CUDART_INF_F;
+        for (int c = 0; c < chunks.total; ++c) top = fmaxf(top, of_head[2 * c]);
+        float sum = 0.0f;
+        for (int c = 0; c < chunks.total; ++c) sum += of_head[2 * c + 1] * expf(of_head[2 * c] - top);
+        maxima[head] = top;
+        sums[head] = sum;
+    }
+    if (talk != nullptr)
+        for (int i = threadIdx.x; i < heads * heads; i += blockDim.x) talk_shared[i] = talk[i];
+    __syncthreads();
+    for (int item = threadIdx.x; item < heads * kChunk; item += blockDim.x) {
+        const int head = item / kChunk, key = item % kChunk;
+        const float score = scores[(((size_t)seq * heads + head) * max_chunks + index) * kChunk + key];
+        weights[item] = expf(score - maxima[head]) / sums[head];  // exp(-inf) = 0 for an invisible key
+    }
+    __syncthreads();
+    const float* applied = weights;
+    if (talk != nullptr) {
+        for (int item = threadIdx.x; item < heads * kChunk; item += blockDim.x) {
+            const int head = item / kChunk, key = item % kChunk;
+            float sum = 0.0f;
+            for (int g = 0; g < heads; ++g) sum = fmaf(talk_shared[head * heads + g], weights[g * kChunk + key], sum);
+            mixed[item] = sum;
+        }
+        __syncthreads();
+        applied = mixed;
+    }
+    const size_t page = block_table[(size_t)seq * max_blocks + first / page_size];
+    const size_t page_base = page * kv_heads * page_size + (first % page_size);
+    const int first_key = begin > first ? begin - first : 0;
+    const int last_key = end - first < kChunk ? end - first : kChunk;
+    float* mine = partial + ((size_t)seq * max_chunks + index) * outputs;
+    for (int o = threadIdx.x; o < outputs; o += blockDim.x) {
+        const int head = o / value_dim, d = o % value_dim;
+        const T* v_col = v_pool + (page_base + (size_t)(head / group) * page_size) * value_dim + d;
+        const float* w = applied + head * kChunk;
+        float sum = 0.0f;
+        for (int key = first_key; key < last_key; ++key) sum = fmaf(w[key], Num<T>::load(v_col + (size_t)key * value_dim), sum);
+        mine[o] = sum;
+    }
+    // the last block of the sequence to get here adds the chunks' parts, in chunk order
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) last_block = atomicAdd(tickets + seq, 1) == chunks.total - 1;
+    __syncthreads();
+    if (!last_block) return;
+    __threadfence();
+    const int row = cu_q[seq];
+    const float* parts = partial + (size_t)seq * max_chunks * outputs;
+    for (int o = threadIdx.x; o < outputs; o += blockDim.x) {
+        float sum = 0.0f;
+        for (int c = 0; c < chunks.total; ++c) sum += __ldcg(parts + (size_t)c * outputs + o);
+        float value = sum * out_scale;
+        if (gate_in != nullptr) {
+            const float z = Num<T>::load(gate_in + (size_t)row * gate_stride + o / value_dim);
+            value *= 1.0f / (1.0f + expf(-z));
+        }
+        Num<T>::store(out + (size_t)row * out_stride + o, value);
+    }
+    if (threadIdx.x == 0) tickets[seq] = 0;  // as the next call expects it
+}
+
 }  // namespace mb
 
 using namespace mb;
@@ -261,6 +420,78 @@ MB_EXPORT int mb_rotate_store(void* q, int q_stride, const void* k, int k_stride
     else
         return fail("rotate_store: unknown dtype code %d", dtype);
     return check_launch("rotate_store");
+}
+
+// One query token per sequence (row cu_q[s] of q), the visible keys of every sequence cut into chunks of 32 with a
+// block each.  most_positions: an upper bound of every sequence's cache length (it sizes grid and scratch).
+// scratch: at least mb_talking_decode_scratch_floats(...) floats; tickets: `sequences` ints that are zero (the
+// call leaves them zero).
+MB_EXPORT size_t mb_talking_decode_chunks(int most_positions, int window, int keep_first) {
+    const int span = (window > 0 && window < most_positions) ? window : most_positions;
+    const int kept = keep_first < most_positions ? keep_first : most_positions;
+    return (size_t)((span + kChunk - 2) / kChunk + 1 + (kept + kChunk - 1) / kChunk);
+}
+
+MB_EXPORT size_t mb_talking_decode_scratch_floats(int sequences, int heads, int value_dim, int most_positions, int window,
+                                                  int keep_first) {
+    const size_t chunks = mb_talking_decode_chunks(most_positions, window, keep_first);
+    return (size_t)sequences * chunks * ((size_t)heads * (kChunk + 2) + (size_t)heads * value_dim);
+}
+
+MB_EXPORT int mb_talking_attention_decode(const void* q, int q_stride, void* out, int out_stride, int dtype, const void* k_pool,
+                                          const void* v_pool, const int* block_table, int max_blocks, const int* cu_q,
+                                          const int* kv_lens, int sequences, int most_positions, const float* talk,
+                                          const void* gate_in, int gate_stride, int heads, int kv_heads, int head_dim,
+                                          int value_dim, int page_size, int window, int keep_first, float scale, float out_scale,
+                                          float* scratch, int* tickets, cudaStream_t stream) {
+    if (sequences <= 0) return 0;
+    if (heads <= 0 || kv_heads <= 0 || heads % kv_heads)
+        return fail("talking_attention: %d heads are no multiple of %d kv heads", heads, kv_heads);
+    if (head_dim <= 0 || value_dim <= 0) return fail("talking_attention: head sizes must be positive");
+    if (page_size <= 0 || page_size % kChunk) return fail("talking_attention: page_size %d must be a multiple of %d", page_size, kChunk);
+    if (window < 0 || keep_first < 0 || most_positions <= 0) return fail("talking_attention: window, keep_first or positions out of range");
+    if (sequences > 65535) return fail("talking_attention: %d sequences exceed the grid limit 65535", sequences);
+    if (!scratch || !tickets) return fail("talking_attention: the decode form needs scratch memory and tickets");
+    const int max_chunks = (int)mb_talking_decode_chunks(most_positions, window, keep_first);
+    float* scores = scratch;
+    float* stats = scores + (size_t)sequences * heads * max_chunks * kChunk;
+    float* partial = stats + (size_t)sequences * heads * max_chunks * 2;
+    const dim3 grid(max_chunks, sequences);
+    const size_t q_bytes = sizeof(float) * (size_t)heads * head_dim;
+    const size_t smem = sizeof(float) * (2 * (size_t)heads * kChunk + 2 * heads + (size_t)heads * heads);
+    if (q_bytes > 200 * 1024 || smem > 200 * 1024) return fail("talking_attention: %d heads of %d do not fit a block's shared memory", heads, head_dim);
+    const int outputs = heads * value_dim;
+    int threads = 128;
+    while (threads < kMaxThreads && threads * 4 < outputs) threads *= 2;
+    cudaError_t status = cudaSuccess;
+    if (dtype == MB_F32) {
+        auto first = talking_decode_scores_kernel<float>;
+        auto second = talking_decode_values_kernel<float>;
+        if (q_bytes > 48 * 1024) status = cudaFuncSetAttribute(first, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)q_bytes);
+        if (status == cudaSuccess && smem > 48 * 1024) status = cudaFuncSetAttribute(second, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (status != cudaSuccess) return fail("talking_attention: %s", cudaGetErrorString(status));
+        first<<<grid, 128, q_bytes, stream>>>((const float*)q, q_stride, (const float*)k_pool, block_table, max_blocks, cu_q, kv_lens,
+                                             scores, stats, max_chunks, heads, kv_heads, head_dim, page_size, window, keep_first, scale);
+        second<<<grid, threads, smem, stream>>>((float*)out, out_stride, (const float*)v_pool, block_table, max_blocks, cu_q, kv_lens,
+                                               scores, stats, partial, tickets, max_chunks, talk, (const float*)gate_in, gate_stride,
+                                               heads, kv_heads, value_dim, page_size, window, keep_first, out_scale);
+    } else if (dtype == MB_BF16) {
+        auto first = talking_decode_scores_kernel<__nv_bfloat16>;
+        auto second = talking_decode_values_kernel<__nv_bfloat16>;
+        if (q_bytes > 48 * 1024) status = cudaFuncSetAttribute(first, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)q_bytes);
+        if (status == cudaSuccess && smem > 48 * 1024) status = cudaFuncSetAttribute(second, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (status != cudaSuccess) return fail("talking_attention: %s", cudaGetErrorString(status));
+        first<<<grid, 128, q_bytes, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool, block_table, max_blocks,
+                                             cu_q, kv_lens, scores, stats, max_chunks, heads, kv_heads, head_dim, page_size, window,
+                                             keep_first, scale);
+        second<<<grid, threads, smem, stream>>>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)v_pool, block_table, max_blocks,
+                                               cu_q, kv_lens, scores, stats, partial, tickets, max_chunks, talk,
+                                               (const __nv_bfloat16*)gate_in, gate_stride, heads, kv_heads, value_dim, page_size,
+                                               window, keep_first, out_scale);
+    } else {
+        return fail("talking_attention: unknown dtype code %d", dtype);
+    }
+    return check_launch("talking_attention_decode");
 }
 
 // q: [tokens, >= heads*head_dim] rows (row stride in elements); out: [tokens, >= heads*value_dim] rows.

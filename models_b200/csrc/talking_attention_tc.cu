@@ -11,7 +11,8 @@
 //           warp mixes its own head's weights from all heads' in float, splits them into two bfloat16
 //           numbers (w' = hi + lo, which keeps about 16 bits of the float weight) and adds
 //           hi . V_c + lo . V_c into its output accumulator.
-// Keys and values of a chunk are copied to shared memory once per block for all key/value heads.
+// Keys and values of a chunk are copied to shared memory once per block for all key/value heads, the next
+// chunk's (cp.async, two stages) while the current one is worked on.
 // Scores, weights, the mixing and every sum are float; only the operands of the products are bfloat16.
 #include "common.cuh"
 
@@ -64,20 +65,49 @@ __device__ __forceinline__ float quad_sum(float v) {
     return v + __shfl_xor_sync(0xffffffffu, v, 2);
 }
 
-// 32 positions of one page, every key/value head, into padded rows [head][32][row bytes].  Rows of positions
-// beyond `last_pos` become zeros when `zero_beyond` (values: a weight of zero must meet a finite number).
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool real) {
+    const int bytes = real ? 16 : 0;  // 0: sixteen zero bytes are written and nothing is read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+// 32 positions of one page, every key/value head, asked for into padded rows [head][32][row bytes].  Rows of
+// positions beyond `last_pos` become zeros when `zero_beyond` (values: a weight of zero must meet a finite number).
 template <int kDim, int kRowBytes>
-__device__ __forceinline__ void load_chunk(unsigned char* dst, const bf16* __restrict__ pool, size_t page, int kv_heads,
+__device__ __forceinline__ void load_chunk(uint32_t dst, const bf16* __restrict__ pool, size_t page, int kv_heads,
                                            int page_size, int offset, int first_key, int last_pos, bool zero_beyond) {
     constexpr int kPieces = kDim / 8;
     for (int i = threadIdx.x; i < kv_heads * kKeys * kPieces; i += kThreads) {
         const int piece = i % kPieces, row = (i / kPieces) % kKeys, head = i / (kPieces * kKeys);
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (!zero_beyond || first_key + row <= last_pos)
-            v = *reinterpret_cast<const uint4*>(pool + ((page * kv_heads + head) * page_size + offset + row) * (size_t)kDim + piece * 8);
-        *reinterpret_cast<uint4*>(dst + (size_t)(head * kKeys + row) * kRowBytes + piece * 16) = v;
+        cp_async16(dst + (head * kKeys + row) * kRowBytes + piece * 16,
+                   pool + ((page * kv_heads + head) * page_size + offset + row) * (size_t)kDim + piece * 8,
+                   !zero_beyond || first_key + row <= last_pos);
     }
 }
+
+// The chunks of 32 positions a tile of queries walks: those of the kept first positions [0, kept_end), then those
+// from the first position the tile's first row sees in its window to the tile's last row.
+struct TileChunks {
+    int window_first, kept_end, last_pos, kept_chunks, total;
+    __device__ __forceinline__ TileChunks(int pos0, int last, int window, int keep_first) {
+        last_pos = last;
+        window_first = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+        kept_end = keep_first < window_first ? keep_first : window_first;
+        kept_chunks = (kept_end + kKeys - 1) / kKeys;
+        total = kept_chunks + last_pos / kKeys - window_first / kKeys + 1;
+    }
+    __device__ __forceinline__ void chunk(int index, int& first, int& begin, int& end) const {
+        if (index < kept_chunks) {
+            first = index * kKeys, begin = 0, end = kept_end;
+        } else {
+            first = (window_first / kKeys + index - kept_chunks) * kKeys, begin = window_first, end = last_pos + 1;
+        }
+    }
+};
 
 // S[16 x 32 keys] of one warp's head: four accumulators of 8 keys.
 __device__ __forceinline__ void chunk_scores(float (&s)[4][4], uint32_t q_rows, uint32_t k_rows) {
@@ -119,9 +149,9 @@ talking_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __re
     const int kv_head = head / (H / kv_heads);
 
     unsigned char* q_smem = smem;                                            // [H][16][kKRow]
-    unsigned char* k_smem = q_smem + (size_t)H * kRows * kKRow;             // [kv_heads][32][kKRow]
-    unsigned char* v_smem = k_smem + (size_t)kv_heads * kKeys * kKRow;      // [kv_heads][32][kVRow]
-    float* w_smem = reinterpret_cast<float*>(v_smem + (size_t)kv_heads * kKeys * kVRow);  // [H][16][32]
+    unsigned char* k_smem = q_smem + (size_t)H * kRows * kKRow;             // two stages of [kv_heads][32][kKRow]
+    unsigned char* v_smem = k_smem + 2 * (size_t)kv_heads * kKeys * kKRow;  // two stages of [kv_heads][32][kVRow]
+    float* w_smem = reinterpret_cast<float*>(v_smem + 2 * (size_t)kv_heads * kKeys * kVRow);  // [H][16][32]
     float* talk_smem = w_smem + H * kWeightFloats;                          // [H][H]
 
     // queries: a row beyond the step's tokens repeats the last one (it is computed and not stored)
@@ -145,21 +175,36 @@ talking_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __re
         row_pos[r] = pos0 + (row < valid ? row : valid - 1);
         row_first[r] = (window > 0 && row_pos[r] - window + 1 > 0) ? row_pos[r] - window + 1 : 0;
     }
-    const int window_first = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;  // of the tile's first row
-    const int kept_end = keep_first < window_first ? keep_first : window_first;
+    const TileChunks chunks(pos0, last_pos, window, keep_first);
+    const int k_stage = kv_heads * kKeys * kKRow, v_stage = kv_heads * kKeys * kVRow;
     const float scale_log2 = scale * 1.4426950408889634f;
     const int* table = block_table + (size_t)seq * max_blocks;
     const uint32_t q_rows = smem_u32(q_smem) + head * kRows * kKRow;
-    const uint32_t k_rows = smem_u32(k_smem) + kv_head * kKeys * kKRow;
-    const uint32_t v_rows = smem_u32(v_smem) + kv_head * kKeys * kVRow;
+    const uint32_t k_base = smem_u32(k_smem), v_base = smem_u32(v_smem);
 
     // walk 1: maximum and sum of every row of every head
     float run_max[2] = {-CUDART_INF_F, -CUDART_INF_F}, run_sum[2] = {0.0f, 0.0f};
-    for (int range = 0; range < 2; ++range) {
-        const int begin = range == 0 ? 0 : window_first, end = range == 0 ? kept_end : last_pos + 1;
-        for (int chunk = begin - begin % kKeys; chunk < end; chunk += kKeys) {
-            load_chunk<D, kKRow>(k_smem, k_pool, table[chunk / page_size], kv_heads, page_size, chunk % page_size, chunk, last_pos, false);
+    {
+        int first, begin, end;
+        chunks.chunk(0, first, begin, end);
+        load_chunk<D, kKRow>(k_base, k_pool, table[first / page_size], kv_heads, page_size, first % page_size, first, last_pos, false);
+        cp_async_commit();
+    }
+    for (int index = 0; index < chunks.total; ++index) {
+        {
+            int chunk, begin, end;
+            if (index + 1 < chunks.total) {  // the next chunk's keys are under way while this one's scores are taken
+                chunks.chunk(index + 1, chunk, begin, end);
+                load_chunk<D, kKRow>(k_base + ((index + 1) & 1) * k_stage, k_pool, table[chunk / page_size], kv_heads, page_size,
+                                     chunk % page_size, chunk, last_pos, false);
+                cp_async_commit();
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
             __syncthreads();
+            chunks.chunk(index, chunk, begin, end);
+            const uint32_t k_rows = k_base + (index & 1) * k_stage + kv_head * kKeys * kKRow;
             float s[4][4];
             chunk_scores(s, q_rows, k_rows);
             float part_max[2] = {-CUDART_INF_F, -CUDART_INF_F};
@@ -182,7 +227,7 @@ talking_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __re
                 run_sum[r] = run_sum[r] * exp2f(run_max[r] - safe) + local;
                 run_max[r] = new_max;
             }
-            __syncthreads();
+            __syncthreads();  // the chunk after the next one is copied over this one
         }
     }
     float inv_sum[2];
@@ -193,13 +238,32 @@ talking_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __re
     float o[DV / 8][4];
 #pragma unroll
     for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
-    for (int range = 0; range < 2; ++range) {
-        const int begin = range == 0 ? 0 : window_first, end = range == 0 ? kept_end : last_pos + 1;
-        for (int chunk = begin - begin % kKeys; chunk < end; chunk += kKeys) {
-            const size_t page = table[chunk / page_size];
-            load_chunk<D, kKRow>(k_smem, k_pool, page, kv_heads, page_size, chunk % page_size, chunk, last_pos, false);
-            load_chunk<DV, kVRow>(v_smem, v_pool, page, kv_heads, page_size, chunk % page_size, chunk, last_pos, true);
+    {
+        int first, begin, end;
+        chunks.chunk(0, first, begin, end);
+        const size_t page = table[first / page_size];
+        load_chunk<D, kKRow>(k_base, k_pool, page, kv_heads, page_size, first % page_size, first, last_pos, false);
+        load_chunk<DV, kVRow>(v_base, v_pool, page, kv_heads, page_size, first % page_size, first, last_pos, true);
+        cp_async_commit();
+    }
+    for (int index = 0; index < chunks.total; ++index) {
+        {
+            int chunk, begin, end;
+            if (index + 1 < chunks.total) {
+                chunks.chunk(index + 1, chunk, begin, end);
+                const size_t page = table[chunk / page_size];
+                const int stage = (index + 1) & 1;
+                load_chunk<D, kKRow>(k_base + stage * k_stage, k_pool, page, kv_heads, page_size, chunk % page_size, chunk, last_pos, false);
+                load_chunk<DV, kVRow>(v_base + stage * v_stage, v_pool, page, kv_heads, page_size, chunk % page_size, chunk, last_pos, true);
+                cp_async_commit();
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
             __syncthreads();
+            chunks.chunk(index, chunk, begin, end);
+            const uint32_t k_rows = k_base + (index & 1) * k_stage + kv_head * kKeys * kKRow;
+            const uint32_t v_rows = v_base + (index & 1) * v_stage + kv_head * kKeys * kVRow;
             float s[4][4];
             chunk_scores(s, q_rows, k_rows);
 #pragma unroll
@@ -248,7 +312,7 @@ talking_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __re
                     mma_bf16(o[2 * dp + 1], lo, b[2], b[3]);
                 }
             }
-            __syncthreads();  // the next chunk overwrites keys, values and weights
+            __syncthreads();  // the next chunk overwrites the weights, the one after it these keys and values
         }
     }
 
@@ -275,7 +339,7 @@ talking_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __re
 using namespace mb;
 
 static size_t block_bytes(int kv_heads) {
-    return (size_t)H * kRows * kKRow + (size_t)kv_heads * kKeys * (kKRow + kVRow) + sizeof(float) * ((size_t)H * kWeightFloats + H * H);
+    return (size_t)H * kRows * kKRow + 2 * (size_t)kv_heads * kKeys * (kKRow + kVRow) + sizeof(float) * ((size_t)H * kWeightFloats + H * H);
 }
 
 MB_EXPORT size_t mb_talking_attention_tc_block_bytes(int kv_heads) { return block_bytes(kv_heads); }

@@ -368,6 +368,19 @@ def rotate_store(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, positions: t
                                   head_dim, value_dim, rotary_dim, page_size, _stream()))
 
 
+_tickets = {}  # device -> every ticket array handed out so far (captured steps keep using theirs), the last one current
+
+
+def _zero_tickets(device, count: int) -> torch.Tensor:
+    """`count` int32 zeros that the kernels that take tickets leave zero again, so that one array serves every call
+    on the device's streams in turn."""
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    arrays = _tickets.setdefault(key, [])
+    if not arrays or arrays[-1].numel() < count:
+        arrays.append(torch.zeros(max(count, 256), dtype=torch.int32, device=device))
+    return arrays[-1]
+
+
 def talking_attention_tc_library(heads: int, head_dim: int, value_dim: int):
     """The tensor-core form, compiled for this head count and these key and value sizes at first use."""
     return load_library("mb_talking_attention_tc", ["talking_attention_tc.cu"],
@@ -381,14 +394,14 @@ def talking_attention_tc_takes(q: torch.Tensor, out: torch.Tensor, k_pool: torch
                                kv_heads: int, head_dim: int, value_dim: int, max_q_len: int) -> bool:
     """bfloat16; one warp per head, so at most 16 heads; key and value sizes multiples of 16, with values no wider
     than the registers of a block of that many warps hold as an accumulator; 16-byte query rows; and a block's
-    shared memory (queries of 16 tokens, a chunk of keys and values of every key/value head, the heads' weights)."""
+    shared memory (queries of 16 tokens, two chunks of keys and values of every key/value head, the heads' weights)."""
     if q.dtype != torch.bfloat16 or max_q_len < TALKING_TC_MIN_ROWS or not 1 <= heads <= 16:
         return False
     if head_dim % 16 or value_dim % 16 or not 16 <= head_dim <= 256 or not 16 <= value_dim <= (256 if heads <= 8 else 128):
         return False
     if q.stride(0) % 8 or out.stride(0) % 2 or q.data_ptr() % 16 or out.data_ptr() % 4 or k_pool.data_ptr() % 16 or v_pool.data_ptr() % 16:
         return False
-    block = (heads * 16 * (2 * head_dim + 16) + kv_heads * 32 * (2 * head_dim + 2 * value_dim + 32) + 4 * (heads * 512 + heads * heads))
+    block = (heads * 16 * (2 * head_dim + 16) + 2 * kv_heads * 32 * (2 * head_dim + 2 * value_dim + 32) + 4 * (heads * 512 + heads * heads))
     return block <= 227 * 1024
 
 
@@ -396,14 +409,17 @@ def talking_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, 
                       block_table: torch.Tensor, cu_q: torch.Tensor, kv_lens: torch.Tensor, max_q_len: int, heads: int,
                       kv_heads: int, head_dim: int, value_dim: int, window: Optional[int], keep_first: int, scale: float,
                       talk: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, out_scale: float = 1.0,
-                      kernel: Optional[str] = None) -> None:
+                      kernel: Optional[str] = None, most_positions: Optional[int] = None) -> None:
     """Causal attention over the paged cache with softmax weights mixed across heads by `talk` (float32
     [heads, heads]; None: not mixed), a window that also keeps the first `keep_first` positions, value heads
     of `value_dim`, and an output gate: out_h = out_scale * sigmoid(gate[:, h]) * sum_j w'_h(j) v(j).
     q [T, heads*head_dim], out [T, heads*value_dim], gate [T, heads] (or None) may be column slices.
-    `kernel`: None picks the tensor-core form where it applies (bfloat16 steps of many tokens), else the
-    form with a block per token; "tc" or "rows" asks for one of them."""
-    if kernel not in (None, "tc", "rows"):
+    `kernel`: None picks the decode form for steps of one token per sequence (the visible keys cut into chunks
+    with a block each; `most_positions`, a bound of every sequence's cache length that does not change from
+    step to step, sizes its grid: by default what the page table can address), the tensor-core form where it
+    applies (bfloat16 steps of many tokens), else the form with a block per token; "decode", "tc" or "rows" asks
+    for one of them."""
+    if kernel not in (None, "tc", "rows", "decode"):
         raise KernelError(f"talking_attention: unknown kernel {kernel!r}")
     _cuda(q, out, k_pool, v_pool, block_table, cu_q, kv_lens, talk, gate)
     _int32(block_table, "block_table")
@@ -426,6 +442,22 @@ def talking_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, 
         _columns(gate, "gate")
         if gate.dtype != q.dtype or tuple(gate.shape) != (q.shape[0], heads):
             raise KernelError(f"gate must be [{q.shape[0]}, {heads}] of q's dtype")
+    if kernel == "decode" or (kernel is None and max_q_len == 1):
+        if max_q_len != 1:
+            raise KernelError("the decode form takes one token per sequence")
+        sequences = kv_lens.numel()
+        bound = most_positions or block_table.shape[1] * page_size
+        lib = talking_attention_library()
+        lib.mb_talking_decode_scratch_floats.restype = ctypes.c_size_t
+        scratch = torch.empty((lib.mb_talking_decode_scratch_floats(sequences, heads, value_dim, bound, window or 0, keep_first),),
+                              dtype=torch.float32, device=q.device)
+        _run(lib, lib.mb_talking_attention_decode(
+            _p(q), q.stride(0), _p(out), out.stride(0), _code(q.dtype), _p(k_pool), _p(v_pool), _p(block_table),
+            block_table.shape[1], _p(cu_q), _p(kv_lens), sequences, bound, _p(talk), _p(gate),
+            gate.stride(0) if gate is not None else 0, heads, kv_heads, head_dim, value_dim, page_size, window or 0, keep_first,
+            ctypes.c_float(scale), ctypes.c_float(out_scale), _p(scratch), _p(_zero_tickets(q.device, sequences)), _stream()))
+        _launches[0] += 1  # two kernels
+        return
     if kernel == "tc" or (kernel is None and talking_attention_tc_takes(q, out, k_pool, v_pool, heads, kv_heads, head_dim, value_dim,
                                                                       max_q_len)):
         if q.dtype != torch.bfloat16:

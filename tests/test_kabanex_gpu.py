@@ -120,8 +120,9 @@ def test_one_key_decides_the_attention(cuda_device, tokens, window, keep_first, 
         assert scaled_error(got, expected) < tol, kernel
         part = _attend(q, k, v, talk, gate, 0.5, window, keep_first, dtype, cuda_device, q_len=37, kernel=kernel)  # a portion
         assert scaled_error(part, expected[-37:]) < tol, kernel
-    last = _attend(q, k, v, talk, gate, 0.5, window, keep_first, dtype, cuda_device, q_len=1)  # as a decode step sees it
-    assert scaled_error(last[0], expected[-1]) < tol
+    for kernel in ("decode", "rows"):  # as a decode step sees it: the keys' chunks with a block each; a block for the token
+        last = _attend(q, k, v, talk, gate, 0.5, window, keep_first, dtype, cuda_device, q_len=1, kernel=kernel)
+        assert scaled_error(last[0], expected[-1]) < tol, kernel
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
