@@ -337,6 +337,8 @@ inline int grid_for(size_t total, int block) {
 template <typename Out>
 __global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ weight, const float* __restrict__ bias,
                                  Out* __restrict__ out, const int* __restrict__ rows, int width, float eps, int cached) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     __shared__ float scratch[32];
     extern __shared__ float kept[];
     const int source = rows != nullptr ? rows[blockIdx.x] : blockIdx.x;
@@ -371,6 +373,8 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
 template <typename T>
 __global__ void activate_kernel(const T* __restrict__ src, int src_stride, T* __restrict__ dst, int dst_stride, int cols,
                                 size_t total, int activation, float scale) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t r = i / cols, c = i % cols;
         Num<T>::store(dst + r * dst_stride + c, scale * gate_activation(activation, Num<T>::load(src + r * src_stride + c)));
@@ -505,9 +509,15 @@ MB_EXPORT int mb_layernorm(const float* x, const float* weight, const float* bia
     const int cached = width <= 10240 ? 1 : 0;  // 40 KB of a block's shared memory
     const size_t smem = cached ? sizeof(float) * (size_t)width : 0;
     if (out_dtype == MB_F32)
-        layernorm_kernel<float><<<out_rows, threads, smem, stream>>>(x, weight, bias, (float*)out, rows, width, eps, cached);
+        {
+            const int status = launch_dependent("elementwise", layernorm_kernel<float>, dim3(out_rows), dim3(threads), smem, stream, true, x, weight, bias, (float*)out, rows, width, eps, cached);
+            if (status) return status;
+        }
     else if (out_dtype == MB_BF16)
-        layernorm_kernel<__nv_bfloat16><<<out_rows, threads, smem, stream>>>(x, weight, bias, (__nv_bfloat16*)out, rows, width, eps, cached);
+        {
+            const int status = launch_dependent("elementwise", layernorm_kernel<__nv_bfloat16>, dim3(out_rows), dim3(threads), smem, stream, true, x, weight, bias, (__nv_bfloat16*)out, rows, width, eps, cached);
+            if (status) return status;
+        }
     else
         return fail("layernorm: unknown dtype code %d", out_dtype);
     return check_launch("layernorm");
@@ -522,11 +532,17 @@ MB_EXPORT int mb_activate(const void* src, int src_stride, void* dst, int dst_st
     const size_t blocks = (total + 255) / 256;
     const int grid = (int)(blocks > 148 * 32 ? 148 * 32 : blocks);
     if (dtype == MB_F32)
-        activate_kernel<float><<<grid, 256, 0, stream>>>((const float*)src, src_stride, (float*)dst, dst_stride, cols, total,
+        {
+            const int status = launch_dependent("elementwise", activate_kernel<float>, dim3(grid), dim3(256), 0, stream, true, (const float*)src, src_stride, (float*)dst, dst_stride, cols, total,
                                                        activation, scale);
+            if (status) return status;
+        }
     else if (dtype == MB_BF16)
-        activate_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)src, src_stride, (__nv_bfloat16*)dst,
+        {
+            const int status = launch_dependent("elementwise", activate_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, true, (const __nv_bfloat16*)src, src_stride, (__nv_bfloat16*)dst,
                                                                dst_stride, cols, total, activation, scale);
+            if (status) return status;
+        }
     else
         return fail("activate: unknown dtype code %d", dtype);
     return check_launch("activate");

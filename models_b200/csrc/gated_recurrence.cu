@@ -29,6 +29,8 @@ __global__ void mingru_scan_kernel(const T* __restrict__ zin, const T* __restric
                                    int in_stride, const float* __restrict__ z_bias, const float* __restrict__ x_bias,
                                    float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu_q,
                                    int width, T* __restrict__ out, int out_stride, float out_scale) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     __shared__ float a_of[kMaxChunks][kChannels];
     __shared__ float b_of[kMaxChunks][kChannels];
     const int seq = blockIdx.y;
@@ -42,8 +44,8 @@ __global__ void mingru_scan_kernel(const T* __restrict__ zin, const T* __restric
     const int t0 = min(chunk * per, count), t1 = min(t0 + per, count);
     const float bz = live ? z_bias[channel] : 0.0f, bx = live ? x_bias[channel] : 0.0f;
 
-    // Loads do not depend on the recurrence: four tokens' inputs are asked for before the first is used.
-    constexpr int kAhead = 4;
+    // Loads do not depend on the recurrence: eight tokens' inputs are asked for before the first is used.
+    constexpr int kAhead = 8;
     if (chunks > 1) {
         float a = 1.0f, b = 0.0f;
         if (live) {
@@ -127,13 +129,19 @@ MB_EXPORT int mb_mingru_scan(const void* zin, const void* xin, const void* gin, 
     while (chunks < kMaxChunks && chunks * 8 < max_q_len) chunks *= 2;  // runs of at least 8 tokens
     const dim3 grid((width + kChannels - 1) / kChannels, sequences), block(kChannels, chunks);
     if (dtype == MB_F32)
-        mingru_scan_kernel<float><<<grid, block, 0, stream>>>((const float*)zin, (const float*)xin, (const float*)gin, in_stride,
+        {
+            const int status = launch_dependent("mingru_scan", mingru_scan_kernel<float>, dim3(grid), dim3(block), 0, stream, true, (const float*)zin, (const float*)xin, (const float*)gin, in_stride,
                                                             z_bias, x_bias, state, slots, cu_q, width, (float*)out,
                                                             out_stride, out_scale);
+            if (status) return status;
+        }
     else if (dtype == MB_BF16)
-        mingru_scan_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(
+        {
+            const int status = launch_dependent("mingru_scan", mingru_scan_kernel<__nv_bfloat16>, dim3(grid), dim3(block), 0, stream, true, 
             (const __nv_bfloat16*)zin, (const __nv_bfloat16*)xin, (const __nv_bfloat16*)gin, in_stride, z_bias, x_bias, state,
             slots, cu_q, width, (__nv_bfloat16*)out, out_stride, out_scale);
+            if (status) return status;
+        }
     else
         return fail("mingru_scan: unknown dtype code %d", dtype);
     return check_launch("mingru_scan");

@@ -56,6 +56,8 @@ __global__ void rotate_store_kernel(T* __restrict__ q, int q_stride, const T* __
                                     const float* __restrict__ cos_table, const float* __restrict__ sin_table,
                                     T* __restrict__ k_pool, T* __restrict__ v_pool, const int* __restrict__ slot_mapping,
                                     int heads, int kv_heads, int head_dim, int value_dim, int rotary_dim, int page_size) {
+    grid_launch_dependents();  // what follows may start its own preparations; it waits for this grid before it reads
+    grid_dependency_wait();
     const int token = blockIdx.x;
     const int half = rotary_dim / 2;
     const int pos = positions[token];
@@ -104,6 +106,8 @@ __global__ void __launch_bounds__(kMaxThreads) talking_attention_rows_kernel(
     const int* __restrict__ kv_lens, const float* __restrict__ talk, const T* __restrict__ gate_in, int gate_stride,
     int heads, int kv_heads, int head_dim, int value_dim, int page_size, int window, int keep_first, float scale,
     float out_scale) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     extern __shared__ float shared[];
     const int seq = blockIdx.y;
     const int q_begin = cu_q[seq];
@@ -267,6 +271,8 @@ __global__ void __launch_bounds__(128) talking_decode_scores_kernel(
     const T* __restrict__ q, int q_stride, const T* __restrict__ k_pool, const int* __restrict__ block_table, int max_blocks,
     const int* __restrict__ cu_q, const int* __restrict__ kv_lens, float* __restrict__ scores, float* __restrict__ stats,
     int max_chunks, int heads, int kv_heads, int head_dim, int page_size, int window, int keep_first, float scale) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     extern __shared__ float q_shared[];  // heads * head_dim
     const int seq = blockIdx.y, index = blockIdx.x;
     const DecodeChunks chunks(kv_lens[seq], window, keep_first);
@@ -306,6 +312,8 @@ __global__ void __launch_bounds__(kMaxThreads) talking_decode_values_kernel(
     float* __restrict__ partial, int* __restrict__ tickets, int max_chunks, const float* __restrict__ talk,
     const T* __restrict__ gate_in, int gate_stride, int heads, int kv_heads, int value_dim, int page_size, int window,
     int keep_first, float out_scale) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     extern __shared__ float shared[];
     __shared__ int last_block;
     const int seq = blockIdx.y, index = blockIdx.x;
@@ -409,14 +417,20 @@ MB_EXPORT int mb_rotate_store(void* q, int q_stride, const void* k, int k_stride
     const int work = kv_heads * (head_dim > value_dim ? head_dim : value_dim);
     const int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
     if (dtype == MB_F32)
-        rotate_store_kernel<float><<<tokens, threads, 0, stream>>>(
+        {
+            const int status = launch_dependent("talking_attention", rotate_store_kernel<float>, dim3(tokens), dim3(threads), 0, stream, true, 
             (float*)q, q_stride, (const float*)k, k_stride, (const float*)v, v_stride, positions, cos_table, sin_table,
             (float*)k_pool, (float*)v_pool, slot_mapping, heads, kv_heads, head_dim, value_dim, rotary_dim, page_size);
+            if (status) return status;
+        }
     else if (dtype == MB_BF16)
-        rotate_store_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(
+        {
+            const int status = launch_dependent("talking_attention", rotate_store_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream, true, 
             (__nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, positions,
             cos_table, sin_table, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, slot_mapping, heads, kv_heads, head_dim,
             value_dim, rotary_dim, page_size);
+            if (status) return status;
+        }
     else
         return fail("rotate_store: unknown dtype code %d", dtype);
     return check_launch("rotate_store");
@@ -470,24 +484,36 @@ MB_EXPORT int mb_talking_attention_decode(const void* q, int q_stride, void* out
         if (q_bytes > 48 * 1024) status = cudaFuncSetAttribute(first, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)q_bytes);
         if (status == cudaSuccess && smem > 48 * 1024) status = cudaFuncSetAttribute(second, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (status != cudaSuccess) return fail("talking_attention: %s", cudaGetErrorString(status));
-        first<<<grid, 128, q_bytes, stream>>>((const float*)q, q_stride, (const float*)k_pool, block_table, max_blocks, cu_q, kv_lens,
+        {
+            const int status = launch_dependent("talking_attention", first, dim3(grid), dim3(128), q_bytes, stream, true, (const float*)q, q_stride, (const float*)k_pool, block_table, max_blocks, cu_q, kv_lens,
                                              scores, stats, max_chunks, heads, kv_heads, head_dim, page_size, window, keep_first, scale);
-        second<<<grid, threads, smem, stream>>>((float*)out, out_stride, (const float*)v_pool, block_table, max_blocks, cu_q, kv_lens,
+            if (status) return status;
+        }
+        {
+            const int status = launch_dependent("talking_attention", second, dim3(grid), dim3(threads), smem, stream, true, (float*)out, out_stride, (const float*)v_pool, block_table, max_blocks, cu_q, kv_lens,
                                                scores, stats, partial, tickets, max_chunks, talk, (const float*)gate_in, gate_stride,
                                                heads, kv_heads, value_dim, page_size, window, keep_first, out_scale);
+            if (status) return status;
+        }
     } else if (dtype == MB_BF16) {
         auto first = talking_decode_scores_kernel<__nv_bfloat16>;
         auto second = talking_decode_values_kernel<__nv_bfloat16>;
         if (q_bytes > 48 * 1024) status = cudaFuncSetAttribute(first, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)q_bytes);
         if (status == cudaSuccess && smem > 48 * 1024) status = cudaFuncSetAttribute(second, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (status != cudaSuccess) return fail("talking_attention: %s", cudaGetErrorString(status));
-        first<<<grid, 128, q_bytes, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool, block_table, max_blocks,
+        {
+            const int status = launch_dependent("talking_attention", first, dim3(grid), dim3(128), q_bytes, stream, true, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool, block_table, max_blocks,
                                              cu_q, kv_lens, scores, stats, max_chunks, heads, kv_heads, head_dim, page_size, window,
                                              keep_first, scale);
-        second<<<grid, threads, smem, stream>>>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)v_pool, block_table, max_blocks,
+            if (status) return status;
+        }
+        {
+            const int status = launch_dependent("talking_attention", second, dim3(grid), dim3(threads), smem, stream, true, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)v_pool, block_table, max_blocks,
                                                cu_q, kv_lens, scores, stats, partial, tickets, max_chunks, talk,
                                                (const __nv_bfloat16*)gate_in, gate_stride, heads, kv_heads, value_dim, page_size,
                                                window, keep_first, out_scale);
+            if (status) return status;
+        }
     } else {
         return fail("talking_attention: unknown dtype code %d", dtype);
     }
@@ -524,20 +550,26 @@ MB_EXPORT int mb_talking_attention_rows(const void* q, int q_stride, void* out, 
             status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (status != cudaSuccess) return fail("talking_attention: %s", cudaGetErrorString(status));
         }
-        kernel<<<grid, threads, smem, stream>>>(
+        {
+            const int status = launch_dependent("talking_attention", kernel, dim3(grid), dim3(threads), smem, stream, true, 
             (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_pool, (const float*)v_pool, block_table,
             max_blocks, cu_q, kv_lens, talk, (const float*)gate_in, gate_stride, heads, kv_heads, head_dim, value_dim,
             page_size, window, keep_first, scale, out_scale);
+            if (status) return status;
+        }
     } else if (dtype == MB_BF16) {
         auto kernel = talking_attention_rows_kernel<__nv_bfloat16>;
         if (smem > 48 * 1024) {
             status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (status != cudaSuccess) return fail("talking_attention: %s", cudaGetErrorString(status));
         }
-        kernel<<<grid, threads, smem, stream>>>(
+        {
+            const int status = launch_dependent("talking_attention", kernel, dim3(grid), dim3(threads), smem, stream, true, 
             (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool,
             (const __nv_bfloat16*)v_pool, block_table, max_blocks, cu_q, kv_lens, talk, (const __nv_bfloat16*)gate_in,
             gate_stride, heads, kv_heads, head_dim, value_dim, page_size, window, keep_first, scale, out_scale);
+            if (status) return status;
+        }
     } else {
         return fail("talking_attention: unknown dtype code %d", dtype);
     }

@@ -136,6 +136,8 @@ talking_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __re
                             int max_blocks, const int* __restrict__ cu_q, const int* __restrict__ kv_lens,
                             const float* __restrict__ talk, const bf16* __restrict__ gate_in, int gate_stride, int kv_heads,
                             int page_size, int window, int keep_first, float scale, float out_scale) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     extern __shared__ __align__(16) unsigned char smem[];
     const int seq = blockIdx.y;
     const int q_begin = cu_q[seq];
@@ -368,8 +370,11 @@ MB_EXPORT int mb_talking_attention_tc(const void* q, int q_stride, void* out, in
         configured[device] = true;
     }
     const dim3 grid((max_q_len + kRows - 1) / kRows, sequences);
-    talking_attention_tc_kernel<<<grid, kThreads, smem, stream>>>(
+    {
+            const int status = launch_dependent("talking_attention_tc", talking_attention_tc_kernel, dim3(grid), dim3(kThreads), smem, stream, true, 
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table, max_blocks, cu_q,
         kv_lens, talk, (const bf16*)gate_in, gate_stride, kv_heads, page_size, window, keep_first, scale, out_scale);
+            if (status) return status;
+        }
     return check_launch("talking_attention_tc");
 }
