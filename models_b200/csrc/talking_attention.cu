@@ -265,9 +265,9 @@ struct DecodeChunks {
     }
 };
 
-// grid (most chunks of any sequence, sequences); block 128.
+// grid (most chunks of any sequence, sequences); block: a warp per head, at most 16.
 template <typename T>
-__global__ void __launch_bounds__(128) talking_decode_scores_kernel(
+__global__ void __launch_bounds__(kMaxThreads) talking_decode_scores_kernel(
     const T* __restrict__ q, int q_stride, const T* __restrict__ k_pool, const int* __restrict__ block_table, int max_blocks,
     const int* __restrict__ cu_q, const int* __restrict__ kv_lens, float* __restrict__ scores, float* __restrict__ stats,
     int max_chunks, int heads, int kv_heads, int head_dim, int page_size, int window, int keep_first, float scale) {
@@ -329,14 +329,24 @@ __global__ void __launch_bounds__(kMaxThreads) talking_decode_values_kernel(
     const int group = heads / kv_heads;
     const int outputs = heads * value_dim;
 
-    for (int head = threadIdx.x; head < heads; head += blockDim.x) {
-        const float* of_head = stats + ((size_t)seq * heads + head) * max_chunks * 2;
+    // every head's maximum and sum over all chunks: a warp per head, a lane per chunk (and every 32nd after it);
+    // the order of the additions depends on the number of chunks only
+    for (int head = threadIdx.x >> 5; head < heads; head += blockDim.x >> 5) {
+        const float2* of_head = reinterpret_cast<const float2*>(stats) + ((size_t)seq * heads + head) * max_chunks;
+        const int lane = threadIdx.x & 31;
         float top = -CUDART_INF_F;
-        for (int c = 0; c < chunks.total; ++c) top = fmaxf(top, of_head[2 * c]);
+        for (int c = lane; c < chunks.total; c += 32) top = fmaxf(top, of_head[c].x);
+        top = warp_max(top);
         float sum = 0.0f;
-        for (int c = 0; c < chunks.total; ++c) sum += of_head[2 * c + 1] * expf(of_head[2 * c] - top);
-        maxima[head] = top;
-        sums[head] = sum;
+        for (int c = lane; c < chunks.total; c += 32) {
+            const float2 pair = of_head[c];
+            sum += pair.y * expf(pair.x - top);
+        }
+        sum = warp_sum(sum);
+        if (lane == 0) {
+            maxima[head] = top;
+            sums[head] = sum;
+        }
     }
     if (talk != nullptr)
         for (int i = threadIdx.x; i < heads * heads; i += blockDim.x) talk_shared[i] = talk[i];
@@ -477,6 +487,8 @@ MB_EXPORT int mb_talking_attention_decode(const void* q, int q_stride, void* out
     const int outputs = heads * value_dim;
     int threads = 128;
     while (threads < kMaxThreads && threads * 4 < outputs) threads *= 2;
+    int score_threads = 32;
+    while (score_threads < kMaxThreads && score_threads < 32 * heads) score_threads *= 2;
     cudaError_t status = cudaSuccess;
     if (dtype == MB_F32) {
         auto first = talking_decode_scores_kernel<float>;
@@ -485,7 +497,7 @@ MB_EXPORT int mb_talking_attention_decode(const void* q, int q_stride, void* out
         if (status == cudaSuccess && smem > 48 * 1024) status = cudaFuncSetAttribute(second, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (status != cudaSuccess) return fail("talking_attention: %s", cudaGetErrorString(status));
         {
-            const int status = launch_dependent("talking_attention", first, dim3(grid), dim3(128), q_bytes, stream, true, (const float*)q, q_stride, (const float*)k_pool, block_table, max_blocks, cu_q, kv_lens,
+            const int status = launch_dependent("talking_attention", first, dim3(grid), dim3(score_threads), q_bytes, stream, true, (const float*)q, q_stride, (const float*)k_pool, block_table, max_blocks, cu_q, kv_lens,
                                              scores, stats, max_chunks, heads, kv_heads, head_dim, page_size, window, keep_first, scale);
             if (status) return status;
         }
@@ -502,7 +514,7 @@ MB_EXPORT int mb_talking_attention_decode(const void* q, int q_stride, void* out
         if (status == cudaSuccess && smem > 48 * 1024) status = cudaFuncSetAttribute(second, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (status != cudaSuccess) return fail("talking_attention: %s", cudaGetErrorString(status));
         {
-            const int status = launch_dependent("talking_attention", first, dim3(grid), dim3(128), q_bytes, stream, true, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool, block_table, max_blocks,
+            const int status = launch_dependent("talking_attention", first, dim3(grid), dim3(score_threads), q_bytes, stream, true, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool, block_table, max_blocks,
                                              cu_q, kv_lens, scores, stats, max_chunks, heads, kv_heads, head_dim, page_size, window,
                                              keep_first, scale);
             if (status) return status;

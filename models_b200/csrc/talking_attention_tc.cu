@@ -7,7 +7,7 @@
 // w_g(i, j) needs every head's normalised weight.  The visible keys are walked twice in chunks of 32:
 //   walk 1: S_g = Q_g K_c^T per warp, running maximum and sum of every row;
 //   walk 2: S_g again, w_g = exp(S_g - max_g) / sum_g in float, handed to the other warps through shared
-//           memory in the layout of the accumulator registers (lane-major, so nobody meets in a bank); each
+//           memory in the layout of the accumulator registers (16 bytes a lane, so nobody meets in a bank); each
 //           warp mixes its own head's weights from all heads' in float, splits them into two bfloat16
 //           numbers (w' = hi + lo, which keeps about 16 bits of the float weight) and adds
 //           hi . V_c + lo . V_c into its output accumulator.
@@ -277,20 +277,24 @@ talking_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __re
                     s[nt][i] = seen ? exp2f(s[nt][i] * scale_log2 - run_max[r]) * inv_sum[r] : 0.0f;
                 }
             if (talk != nullptr) {
+                float4* shared_weights = reinterpret_cast<float4*>(w_smem);  // [head][accumulator][lane]: 16 bytes a lane
 #pragma unroll
                 for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) w_smem[head * kWeightFloats + (nt * 4 + i) * 32 + lane] = s[nt][i];
+                    shared_weights[(head * 4 + nt) * 32 + lane] = make_float4(s[nt][0], s[nt][1], s[nt][2], s[nt][3]);
                 __syncthreads();
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt)
+                for (int nt = 0; nt < 4; ++nt) {
+                    float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        float sum = 0.0f;
-#pragma unroll
-                        for (int g = 0; g < H; ++g) sum = fmaf(mix[g], w_smem[g * kWeightFloats + (nt * 4 + i) * 32 + lane], sum);
-                        s[nt][i] = sum;
+                    for (int g = 0; g < H; ++g) {
+                        const float4 w = shared_weights[(g * 4 + nt) * 32 + lane];
+                        sum.x = fmaf(mix[g], w.x, sum.x);
+                        sum.y = fmaf(mix[g], w.y, sum.y);
+                        sum.z = fmaf(mix[g], w.z, sum.z);
+                        sum.w = fmaf(mix[g], w.w, sum.w);
                     }
+                    s[nt][0] = sum.x, s[nt][1] = sum.y, s[nt][2] = sum.z, s[nt][3] = sum.w;
+                }
             }
 #pragma unroll
             for (int part = 0; part < 2; ++part) {
