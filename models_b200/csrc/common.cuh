@@ -175,5 +175,12 @@ inline int launch_dependent(const char* what, void (*kernel)(KernelArgs...), dim
 
 }  // namespace mb
 
+// launch_dependent(...) as a statement of a launcher: a failed launch returns its status from the launcher.
+#define MB_LAUNCH(...)                                          \
+    do {                                                        \
+        const int mb_status = mb::launch_dependent(__VA_ARGS__); \
+        if (mb_status) return mb_status;                        \
+    } while (0)
+
 #define MB_DEFINE_LAST_ERROR() \
     MB_EXPORT const char* mb_last_error() { return mb::error_buffer(); }

@@ -509,15 +509,11 @@ MB_EXPORT int mb_layernorm(const float* x, const float* weight, const float* bia
     const int cached = width <= 10240 ? 1 : 0;  // 40 KB of a block's shared memory
     const size_t smem = cached ? sizeof(float) * (size_t)width : 0;
     if (out_dtype == MB_F32)
-        {
-            const int status = launch_dependent("elementwise", layernorm_kernel<float>, dim3(out_rows), dim3(threads), smem, stream, true, x, weight, bias, (float*)out, rows, width, eps, cached);
-            if (status) return status;
-        }
+        MB_LAUNCH("elementwise", layernorm_kernel<float>, dim3(out_rows), dim3(threads), smem, stream, true, x, weight,
+                  bias, (float*)out, rows, width, eps, cached);
     else if (out_dtype == MB_BF16)
-        {
-            const int status = launch_dependent("elementwise", layernorm_kernel<__nv_bfloat16>, dim3(out_rows), dim3(threads), smem, stream, true, x, weight, bias, (__nv_bfloat16*)out, rows, width, eps, cached);
-            if (status) return status;
-        }
+        MB_LAUNCH("elementwise", layernorm_kernel<__nv_bfloat16>, dim3(out_rows), dim3(threads), smem, stream, true, x,
+                  weight, bias, (__nv_bfloat16*)out, rows, width, eps, cached);
     else
         return fail("layernorm: unknown dtype code %d", out_dtype);
     return check_launch("layernorm");
@@ -532,17 +528,12 @@ MB_EXPORT int mb_activate(const void* src, int src_stride, void* dst, int dst_st
     const size_t blocks = (total + 255) / 256;
     const int grid = (int)(blocks > 148 * 32 ? 148 * 32 : blocks);
     if (dtype == MB_F32)
-        {
-            const int status = launch_dependent("elementwise", activate_kernel<float>, dim3(grid), dim3(256), 0, stream, true, (const float*)src, src_stride, (float*)dst, dst_stride, cols, total,
-                                                       activation, scale);
-            if (status) return status;
-        }
+        MB_LAUNCH("elementwise", activate_kernel<float>, dim3(grid), dim3(256), 0, stream, true, (const float*)src,
+                  src_stride, (float*)dst, dst_stride, cols, total, activation, scale);
     else if (dtype == MB_BF16)
-        {
-            const int status = launch_dependent("elementwise", activate_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, true, (const __nv_bfloat16*)src, src_stride, (__nv_bfloat16*)dst,
-                                                               dst_stride, cols, total, activation, scale);
-            if (status) return status;
-        }
+        MB_LAUNCH("elementwise", activate_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, true,
+                  (const __nv_bfloat16*)src, src_stride, (__nv_bfloat16*)dst, dst_stride, cols, total, activation,
+                  scale);
     else
         return fail("activate: unknown dtype code %d", dtype);
     return check_launch("activate");

@@ -18,12 +18,12 @@ MB_DEFINE_LAST_ERROR()
 
 namespace mb {
 
-constexpr int kChannels = 32;
-constexpr int kMaxChunks = 32;
+constexpr int kBlockThreads = 1024;  // channels of a block times runs of a block, at most
+constexpr int kMaxChunks = 128;
 
 __device__ __forceinline__ float sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
 
-// grid (ceil(width / 32), sequences); block (32, chunks).
+// grid (ceil(width / channels), sequences); block (channels, chunks) with channels * chunks <= 1024.
 template <typename T>
 __global__ void mingru_scan_kernel(const T* __restrict__ zin, const T* __restrict__ xin, const T* __restrict__ gin,
                                    int in_stride, const float* __restrict__ z_bias, const float* __restrict__ x_bias,
@@ -31,13 +31,13 @@ __global__ void mingru_scan_kernel(const T* __restrict__ zin, const T* __restric
                                    int width, T* __restrict__ out, int out_stride, float out_scale) {
     grid_launch_dependents();
     grid_dependency_wait();
-    __shared__ float a_of[kMaxChunks][kChannels];
-    __shared__ float b_of[kMaxChunks][kChannels];
+    __shared__ float a_of[kBlockThreads];  // [run][channel of the block]
+    __shared__ float b_of[kBlockThreads];
     const int seq = blockIdx.y;
     const int first = cu_q[seq];
     const int count = cu_q[seq + 1] - first;
     if (count <= 0) return;  // the whole block leaves
-    const int channel = blockIdx.x * kChannels + threadIdx.x;
+    const int channel = blockIdx.x * blockDim.x + threadIdx.x;
     const bool live = channel < width;
     const int chunks = blockDim.y, chunk = threadIdx.y;
     const int per = (count + chunks - 1) / chunks;
@@ -75,14 +75,14 @@ __global__ void mingru_scan_kernel(const T* __restrict__ zin, const T* __restric
                 b = (1.0f - z) * b + z * c;
             }
         }
-        a_of[chunk][threadIdx.x] = a;
-        b_of[chunk][threadIdx.x] = b;
+        a_of[chunk * blockDim.x + threadIdx.x] = a;
+        b_of[chunk * blockDim.x + threadIdx.x] = b;
         __syncthreads();
     }
     if (!live) return;
     float* stored = state + (size_t)slots[seq] * width + channel;
     float s = *stored;
-    for (int before = 0; before < chunk; ++before) s = a_of[before][threadIdx.x] * s + b_of[before][threadIdx.x];
+    for (int before = 0; before < chunk; ++before) s = a_of[before * blockDim.x + threadIdx.x] * s + b_of[before * blockDim.x + threadIdx.x];
     int t = t0;
     for (; t + kAhead <= t1; t += kAhead) {
         float zr[kAhead], xr[kAhead], gr[kAhead];
@@ -125,23 +125,21 @@ MB_EXPORT int mb_mingru_scan(const void* zin, const void* xin, const void* gin, 
                              cudaStream_t stream) {
     if (sequences <= 0 || max_q_len <= 0 || width <= 0) return 0;
     if (sequences > 65535) return fail("mingru_scan: %d sequences exceed the grid limit 65535", sequences);
+    // Runs of about 16 tokens, so that a long prompt is walked by many threads at once; the fewer channels a block
+    // then has (down to 8, which still fills a 16-byte piece of a bfloat16 row), the more blocks there are.
     int chunks = 1;
-    while (chunks < kMaxChunks && chunks * 8 < max_q_len) chunks *= 2;  // runs of at least 8 tokens
-    const dim3 grid((width + kChannels - 1) / kChannels, sequences), block(kChannels, chunks);
+    while (chunks < kMaxChunks && chunks * 16 < max_q_len) chunks *= 2;
+    int channels = chunks == 1 ? 128 : kBlockThreads / chunks;
+    if (channels > 32 && chunks > 1) channels = 32;
+    const dim3 grid((width + channels - 1) / channels, sequences), block(channels, chunks);
     if (dtype == MB_F32)
-        {
-            const int status = launch_dependent("mingru_scan", mingru_scan_kernel<float>, dim3(grid), dim3(block), 0, stream, true, (const float*)zin, (const float*)xin, (const float*)gin, in_stride,
-                                                            z_bias, x_bias, state, slots, cu_q, width, (float*)out,
-                                                            out_stride, out_scale);
-            if (status) return status;
-        }
+        MB_LAUNCH("mingru_scan", mingru_scan_kernel<float>, dim3(grid), dim3(block), 0, stream, true,
+                  (const float*)zin, (const float*)xin, (const float*)gin, in_stride, z_bias, x_bias, state, slots,
+                  cu_q, width, (float*)out, out_stride, out_scale);
     else if (dtype == MB_BF16)
-        {
-            const int status = launch_dependent("mingru_scan", mingru_scan_kernel<__nv_bfloat16>, dim3(grid), dim3(block), 0, stream, true, 
-            (const __nv_bfloat16*)zin, (const __nv_bfloat16*)xin, (const __nv_bfloat16*)gin, in_stride, z_bias, x_bias, state,
-            slots, cu_q, width, (__nv_bfloat16*)out, out_stride, out_scale);
-            if (status) return status;
-        }
+        MB_LAUNCH("mingru_scan", mingru_scan_kernel<__nv_bfloat16>, dim3(grid), dim3(block), 0, stream, true,
+                  (const __nv_bfloat16*)zin, (const __nv_bfloat16*)xin, (const __nv_bfloat16*)gin, in_stride, z_bias,
+                  x_bias, state, slots, cu_q, width, (__nv_bfloat16*)out, out_stride, out_scale);
     else
         return fail("mingru_scan: unknown dtype code %d", dtype);
     return check_launch("mingru_scan");

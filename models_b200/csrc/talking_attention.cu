@@ -378,6 +378,7 @@ __global__ void __launch_bounds__(kMaxThreads) talking_decode_values_kernel(
         const T* v_col = v_pool + (page_base + (size_t)(head / group) * page_size) * value_dim + d;
         const float* w = applied + head * kChunk;
         float sum = 0.0f;
+#pragma unroll 8
         for (int key = first_key; key < last_key; ++key) sum = fmaf(w[key], Num<T>::load(v_col + (size_t)key * value_dim), sum);
         mine[o] = sum;
     }
@@ -392,6 +393,7 @@ __global__ void __launch_bounds__(kMaxThreads) talking_decode_values_kernel(
     const float* parts = partial + (size_t)seq * max_chunks * outputs;
     for (int o = threadIdx.x; o < outputs; o += blockDim.x) {
         float sum = 0.0f;
+#pragma unroll 8
         for (int c = 0; c < chunks.total; ++c) sum += __ldcg(parts + (size_t)c * outputs + o);
         float value = sum * out_scale;
         if (gate_in != nullptr) {
@@ -427,20 +429,15 @@ MB_EXPORT int mb_rotate_store(void* q, int q_stride, const void* k, int k_stride
     const int work = kv_heads * (head_dim > value_dim ? head_dim : value_dim);
     const int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
     if (dtype == MB_F32)
-        {
-            const int status = launch_dependent("talking_attention", rotate_store_kernel<float>, dim3(tokens), dim3(threads), 0, stream, true, 
-            (float*)q, q_stride, (const float*)k, k_stride, (const float*)v, v_stride, positions, cos_table, sin_table,
-            (float*)k_pool, (float*)v_pool, slot_mapping, heads, kv_heads, head_dim, value_dim, rotary_dim, page_size);
-            if (status) return status;
-        }
+        MB_LAUNCH("talking_attention", rotate_store_kernel<float>, dim3(tokens), dim3(threads), 0, stream, true,
+                  (float*)q, q_stride, (const float*)k, k_stride, (const float*)v, v_stride, positions, cos_table,
+                  sin_table, (float*)k_pool, (float*)v_pool, slot_mapping, heads, kv_heads, head_dim, value_dim,
+                  rotary_dim, page_size);
     else if (dtype == MB_BF16)
-        {
-            const int status = launch_dependent("talking_attention", rotate_store_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream, true, 
-            (__nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, positions,
-            cos_table, sin_table, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, slot_mapping, heads, kv_heads, head_dim,
-            value_dim, rotary_dim, page_size);
-            if (status) return status;
-        }
+        MB_LAUNCH("talking_attention", rotate_store_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream,
+                  true, (__nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v,
+                  v_stride, positions, cos_table, sin_table, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool,
+                  slot_mapping, heads, kv_heads, head_dim, value_dim, rotary_dim, page_size);
     else
         return fail("rotate_store: unknown dtype code %d", dtype);
     return check_launch("rotate_store");
@@ -496,36 +493,26 @@ MB_EXPORT int mb_talking_attention_decode(const void* q, int q_stride, void* out
         if (q_bytes > 48 * 1024) status = cudaFuncSetAttribute(first, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)q_bytes);
         if (status == cudaSuccess && smem > 48 * 1024) status = cudaFuncSetAttribute(second, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (status != cudaSuccess) return fail("talking_attention: %s", cudaGetErrorString(status));
-        {
-            const int status = launch_dependent("talking_attention", first, dim3(grid), dim3(score_threads), q_bytes, stream, true, (const float*)q, q_stride, (const float*)k_pool, block_table, max_blocks, cu_q, kv_lens,
-                                             scores, stats, max_chunks, heads, kv_heads, head_dim, page_size, window, keep_first, scale);
-            if (status) return status;
-        }
-        {
-            const int status = launch_dependent("talking_attention", second, dim3(grid), dim3(threads), smem, stream, true, (float*)out, out_stride, (const float*)v_pool, block_table, max_blocks, cu_q, kv_lens,
-                                               scores, stats, partial, tickets, max_chunks, talk, (const float*)gate_in, gate_stride,
-                                               heads, kv_heads, value_dim, page_size, window, keep_first, out_scale);
-            if (status) return status;
-        }
+        MB_LAUNCH("talking_attention", first, dim3(grid), dim3(score_threads), q_bytes, stream, true, (const float*)q,
+                  q_stride, (const float*)k_pool, block_table, max_blocks, cu_q, kv_lens, scores, stats, max_chunks,
+                  heads, kv_heads, head_dim, page_size, window, keep_first, scale);
+        MB_LAUNCH("talking_attention", second, dim3(grid), dim3(threads), smem, stream, true, (float*)out, out_stride,
+                  (const float*)v_pool, block_table, max_blocks, cu_q, kv_lens, scores, stats, partial, tickets,
+                  max_chunks, talk, (const float*)gate_in, gate_stride, heads, kv_heads, value_dim, page_size, window,
+                  keep_first, out_scale);
     } else if (dtype == MB_BF16) {
         auto first = talking_decode_scores_kernel<__nv_bfloat16>;
         auto second = talking_decode_values_kernel<__nv_bfloat16>;
         if (q_bytes > 48 * 1024) status = cudaFuncSetAttribute(first, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)q_bytes);
         if (status == cudaSuccess && smem > 48 * 1024) status = cudaFuncSetAttribute(second, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (status != cudaSuccess) return fail("talking_attention: %s", cudaGetErrorString(status));
-        {
-            const int status = launch_dependent("talking_attention", first, dim3(grid), dim3(score_threads), q_bytes, stream, true, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool, block_table, max_blocks,
-                                             cu_q, kv_lens, scores, stats, max_chunks, heads, kv_heads, head_dim, page_size, window,
-                                             keep_first, scale);
-            if (status) return status;
-        }
-        {
-            const int status = launch_dependent("talking_attention", second, dim3(grid), dim3(threads), smem, stream, true, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)v_pool, block_table, max_blocks,
-                                               cu_q, kv_lens, scores, stats, partial, tickets, max_chunks, talk,
-                                               (const __nv_bfloat16*)gate_in, gate_stride, heads, kv_heads, value_dim, page_size,
-                                               window, keep_first, out_scale);
-            if (status) return status;
-        }
+        MB_LAUNCH("talking_attention", first, dim3(grid), dim3(score_threads), q_bytes, stream, true,
+                  (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool, block_table, max_blocks, cu_q,
+                  kv_lens, scores, stats, max_chunks, heads, kv_heads, head_dim, page_size, window, keep_first, scale);
+        MB_LAUNCH("talking_attention", second, dim3(grid), dim3(threads), smem, stream, true, (__nv_bfloat16*)out,
+                  out_stride, (const __nv_bfloat16*)v_pool, block_table, max_blocks, cu_q, kv_lens, scores, stats,
+                  partial, tickets, max_chunks, talk, (const __nv_bfloat16*)gate_in, gate_stride, heads, kv_heads,
+                  value_dim, page_size, window, keep_first, out_scale);
     } else {
         return fail("talking_attention: unknown dtype code %d", dtype);
     }
@@ -562,26 +549,21 @@ MB_EXPORT int mb_talking_attention_rows(const void* q, int q_stride, void* out, 
             status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (status != cudaSuccess) return fail("talking_attention: %s", cudaGetErrorString(status));
         }
-        {
-            const int status = launch_dependent("talking_attention", kernel, dim3(grid), dim3(threads), smem, stream, true, 
-            (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_pool, (const float*)v_pool, block_table,
-            max_blocks, cu_q, kv_lens, talk, (const float*)gate_in, gate_stride, heads, kv_heads, head_dim, value_dim,
-            page_size, window, keep_first, scale, out_scale);
-            if (status) return status;
-        }
+        MB_LAUNCH("talking_attention", kernel, dim3(grid), dim3(threads), smem, stream, true, (const float*)q,
+                  q_stride, (float*)out, out_stride, (const float*)k_pool, (const float*)v_pool, block_table,
+                  max_blocks, cu_q, kv_lens, talk, (const float*)gate_in, gate_stride, heads, kv_heads, head_dim,
+                  value_dim, page_size, window, keep_first, scale, out_scale);
     } else if (dtype == MB_BF16) {
         auto kernel = talking_attention_rows_kernel<__nv_bfloat16>;
         if (smem > 48 * 1024) {
             status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (status != cudaSuccess) return fail("talking_attention: %s", cudaGetErrorString(status));
         }
-        {
-            const int status = launch_dependent("talking_attention", kernel, dim3(grid), dim3(threads), smem, stream, true, 
-            (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool,
-            (const __nv_bfloat16*)v_pool, block_table, max_blocks, cu_q, kv_lens, talk, (const __nv_bfloat16*)gate_in,
-            gate_stride, heads, kv_heads, head_dim, value_dim, page_size, window, keep_first, scale, out_scale);
-            if (status) return status;
-        }
+        MB_LAUNCH("talking_attention", kernel, dim3(grid), dim3(threads), smem, stream, true, (const __nv_bfloat16*)q,
+                  q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool,
+                  (const __nv_bfloat16*)v_pool, block_table, max_blocks, cu_q, kv_lens, talk,
+                  (const __nv_bfloat16*)gate_in, gate_stride, heads, kv_heads, head_dim, value_dim, page_size, window,
+                  keep_first, scale, out_scale);
     } else {
         return fail("talking_attention: unknown dtype code %d", dtype);
     }

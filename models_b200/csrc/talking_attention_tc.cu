@@ -195,16 +195,14 @@ talking_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __re
     for (int index = 0; index < chunks.total; ++index) {
         {
             int chunk, begin, end;
+            cp_async_wait<0>();
+            __syncthreads();  // this chunk's keys are there, and every warp is done with the chunk before it
             if (index + 1 < chunks.total) {  // the next chunk's keys are under way while this one's scores are taken
                 chunks.chunk(index + 1, chunk, begin, end);
                 load_chunk<D, kKRow>(k_base + ((index + 1) & 1) * k_stage, k_pool, table[chunk / page_size], kv_heads, page_size,
                                      chunk % page_size, chunk, last_pos, false);
                 cp_async_commit();
-                cp_async_wait<1>();
-            } else {
-                cp_async_wait<0>();
             }
-            __syncthreads();
             chunks.chunk(index, chunk, begin, end);
             const uint32_t k_rows = k_base + (index & 1) * k_stage + kv_head * kKeys * kKRow;
             float s[4][4];
@@ -229,9 +227,9 @@ talking_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __re
                 run_sum[r] = run_sum[r] * exp2f(run_max[r] - safe) + local;
                 run_max[r] = new_max;
             }
-            __syncthreads();  // the chunk after the next one is copied over this one
         }
     }
+    __syncthreads();  // the second walk copies over the last chunks of the first
     float inv_sum[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) inv_sum[r] = 1.0f / quad_sum(run_sum[r]);  // every row sees its own position
@@ -251,6 +249,8 @@ talking_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __re
     for (int index = 0; index < chunks.total; ++index) {
         {
             int chunk, begin, end;
+            cp_async_wait<0>();
+            __syncthreads();  // this chunk is there; every warp is done with the chunk before it, its weights included
             if (index + 1 < chunks.total) {
                 chunks.chunk(index + 1, chunk, begin, end);
                 const size_t page = table[chunk / page_size];
@@ -258,11 +258,7 @@ talking_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __re
                 load_chunk<D, kKRow>(k_base + stage * k_stage, k_pool, page, kv_heads, page_size, chunk % page_size, chunk, last_pos, false);
                 load_chunk<DV, kVRow>(v_base + stage * v_stage, v_pool, page, kv_heads, page_size, chunk % page_size, chunk, last_pos, true);
                 cp_async_commit();
-                cp_async_wait<1>();
-            } else {
-                cp_async_wait<0>();
             }
-            __syncthreads();
             chunks.chunk(index, chunk, begin, end);
             const uint32_t k_rows = k_base + (index & 1) * k_stage + kv_head * kKeys * kKRow;
             const uint32_t v_rows = v_base + (index & 1) * v_stage + kv_head * kKeys * kVRow;
@@ -318,7 +314,6 @@ talking_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __re
                     mma_bf16(o[2 * dp + 1], lo, b[2], b[3]);
                 }
             }
-            __syncthreads();  // the next chunk overwrites the weights, the one after it these keys and values
         }
     }
 
@@ -374,11 +369,9 @@ MB_EXPORT int mb_talking_attention_tc(const void* q, int q_stride, void* out, in
         configured[device] = true;
     }
     const dim3 grid((max_q_len + kRows - 1) / kRows, sequences);
-    {
-            const int status = launch_dependent("talking_attention_tc", talking_attention_tc_kernel, dim3(grid), dim3(kThreads), smem, stream, true, 
-        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table, max_blocks, cu_q,
-        kv_lens, talk, (const bf16*)gate_in, gate_stride, kv_heads, page_size, window, keep_first, scale, out_scale);
-            if (status) return status;
-        }
+    MB_LAUNCH("talking_attention_tc", talking_attention_tc_kernel, dim3(grid), dim3(kThreads), smem, stream, true,
+                  (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pool, (const bf16*)v_pool,
+                  block_table, max_blocks, cu_q, kv_lens, talk, (const bf16*)gate_in, gate_stride, kv_heads, page_size,
+                  window, keep_first, scale, out_scale);
     return check_launch("talking_attention_tc");
 }
