@@ -370,6 +370,22 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
         Num<Out>::store(out_row + i, (row[i] - mean) * inv * weight[i] + bias[i]);
 }
 
+// Eight elements a thread (columns and strides are multiples of 8 and the slices start on 16 bytes; 32 for float).
+template <typename T>
+__global__ void activate_vec8_kernel(const T* __restrict__ src, int src_stride, T* __restrict__ dst, int dst_stride, int cols8,
+                                     size_t total8, int activation, float scale) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / cols8, c = (i % cols8) * 8;
+        float v[8];
+        load8(src + r * src_stride + c, v);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = scale * gate_activation(activation, v[k]);
+        store8(dst + r * dst_stride + c, v);
+    }
+}
+
 template <typename T>
 __global__ void activate_kernel(const T* __restrict__ src, int src_stride, T* __restrict__ dst, int dst_stride, int cols,
                                 size_t total, int activation, float scale) {
@@ -525,6 +541,20 @@ MB_EXPORT int mb_activate(const void* src, int src_stride, void* dst, int dst_st
     if (rows <= 0 || cols <= 0) return 0;
     if (activation < 0 || activation >= MB_ACT_COUNT) return fail("activate: unknown activation code %d", activation);
     const size_t total = (size_t)rows * cols;
+    const size_t align = dtype == MB_F32 ? 31 : 15;
+    if (cols % 8 == 0 && src_stride % 8 == 0 && dst_stride % 8 == 0 && !((uintptr_t)src & align) && !((uintptr_t)dst & align)) {
+        const size_t total8 = total / 8, blocks8 = (total8 + 255) / 256;
+        const int grid8 = (int)(blocks8 > 148 * 16 ? 148 * 16 : blocks8);
+        if (dtype == MB_F32)
+            MB_LAUNCH("elementwise", activate_vec8_kernel<float>, dim3(grid8), dim3(256), 0, stream, true, (const float*)src,
+                      src_stride, (float*)dst, dst_stride, cols / 8, total8, activation, scale);
+        else if (dtype == MB_BF16)
+            MB_LAUNCH("elementwise", activate_vec8_kernel<__nv_bfloat16>, dim3(grid8), dim3(256), 0, stream, true,
+                      (const __nv_bfloat16*)src, src_stride, (__nv_bfloat16*)dst, dst_stride, cols / 8, total8, activation, scale);
+        else
+            return fail("activate: unknown dtype code %d", dtype);
+        return check_launch("activate");
+    }
     const size_t blocks = (total + 255) / 256;
     const int grid = (int)(blocks > 148 * 32 ? 148 * 32 : blocks);
     if (dtype == MB_F32)

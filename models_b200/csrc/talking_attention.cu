@@ -30,11 +30,22 @@ constexpr int kChunk = 32;
 constexpr int kMaxAcc = 16;  // outputs per thread: heads * value_dim <= kMaxAcc * threads
 constexpr int kMaxThreads = 512;
 
+// Two neighbouring elements (the address is a multiple of two elements).
+__device__ __forceinline__ void load_pair(const float* p, float& a, float& b) {
+    const float2 v = *reinterpret_cast<const float2*>(p);
+    a = v.x, b = v.y;
+}
+__device__ __forceinline__ void load_pair(const __nv_bfloat16* p, float& a, float& b) {
+    const uint32_t raw = *reinterpret_cast<const uint32_t*>(p);
+    a = __uint_as_float(raw << 16), b = __uint_as_float(raw & 0xffff0000u);
+}
+
 template <typename T>
 __device__ __forceinline__ float dot_row(const float* __restrict__ q_shared, const T* __restrict__ k_row, int head_dim,
                                          bool vector_ok) {
     float sum = 0.0f;
     if (vector_ok) {
+#pragma unroll 4
         for (int d = 0; d < head_dim; d += 8) {
             float kv[8];
             load8(k_row + d, kv);
@@ -373,14 +384,40 @@ __global__ void __launch_bounds__(kMaxThreads) talking_decode_values_kernel(
     const int first_key = begin > first ? begin - first : 0;
     const int last_key = end - first < kChunk ? end - first : kChunk;
     float* mine = partial + ((size_t)seq * max_chunks + index) * outputs;
-    for (int o = threadIdx.x; o < outputs; o += blockDim.x) {
-        const int head = o / value_dim, d = o % value_dim;
-        const T* v_col = v_pool + (page_base + (size_t)(head / group) * page_size) * value_dim + d;
-        const float* w = applied + head * kChunk;
-        float sum = 0.0f;
+    if ((value_dim & 1) == 0) {
+        // A thread owns two neighbouring coordinates of one key/value head: it asks for all 32 keys' values at once
+        // (one round trip to memory), then serves every query head of the group from its registers.
+        const int half = value_dim / 2;
+        for (int item = threadIdx.x; item < kv_heads * half; item += blockDim.x) {
+            const int kv_head = item / half, d = 2 * (item % half);
+            const T* v_col = v_pool + (page_base + (size_t)kv_head * page_size) * value_dim + d;
+            float lo[kChunk], hi[kChunk];
+#pragma unroll
+            for (int key = 0; key < kChunk; ++key) {
+                lo[key] = hi[key] = 0.0f;
+                if (key >= first_key && key < last_key) load_pair(v_col + (size_t)key * value_dim, lo[key], hi[key]);
+            }
+            for (int head = kv_head * group; head < (kv_head + 1) * group; ++head) {
+                const float* w = applied + head * kChunk;
+                float sum_lo = 0.0f, sum_hi = 0.0f;
+#pragma unroll
+                for (int key = 0; key < kChunk; ++key) {  // (the weight of a key outside the range is zero)
+                    sum_lo = fmaf(w[key], lo[key], sum_lo);
+                    sum_hi = fmaf(w[key], hi[key], sum_hi);
+                }
+                *reinterpret_cast<float2*>(mine + head * value_dim + d) = make_float2(sum_lo, sum_hi);
+            }
+        }
+    } else {
+        for (int o = threadIdx.x; o < outputs; o += blockDim.x) {
+            const int head = o / value_dim, d = o % value_dim;
+            const T* v_col = v_pool + (page_base + (size_t)(head / group) * page_size) * value_dim + d;
+            const float* w = applied + head * kChunk;
+            float sum = 0.0f;
 #pragma unroll 8
-        for (int key = first_key; key < last_key; ++key) sum = fmaf(w[key], Num<T>::load(v_col + (size_t)key * value_dim), sum);
-        mine[o] = sum;
+            for (int key = first_key; key < last_key; ++key) sum = fmaf(w[key], Num<T>::load(v_col + (size_t)key * value_dim), sum);
+            mine[o] = sum;
+        }
     }
     // the last block of the sequence to get here adds the chunks' parts, in chunk order
     __threadfence();
@@ -391,16 +428,34 @@ __global__ void __launch_bounds__(kMaxThreads) talking_decode_values_kernel(
     __threadfence();
     const int row = cu_q[seq];
     const float* parts = partial + (size_t)seq * max_chunks * outputs;
-    for (int o = threadIdx.x; o < outputs; o += blockDim.x) {
-        float sum = 0.0f;
+    if ((value_dim & 3) == 0) {
+        for (int o = 4 * threadIdx.x; o < outputs; o += 4 * blockDim.x) {  // four neighbouring coordinates of one head
+            float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll 8
-        for (int c = 0; c < chunks.total; ++c) sum += __ldcg(parts + (size_t)c * outputs + o);
-        float value = sum * out_scale;
-        if (gate_in != nullptr) {
-            const float z = Num<T>::load(gate_in + (size_t)row * gate_stride + o / value_dim);
-            value *= 1.0f / (1.0f + expf(-z));
+            for (int c = 0; c < chunks.total; ++c) {
+                const float4 part = __ldcg(reinterpret_cast<const float4*>(parts + (size_t)c * outputs + o));
+                sum.x += part.x, sum.y += part.y, sum.z += part.z, sum.w += part.w;
+            }
+            float factor = out_scale;
+            if (gate_in != nullptr) factor /= 1.0f + expf(-Num<T>::load(gate_in + (size_t)row * gate_stride + o / value_dim));
+            T* dst = out + (size_t)row * out_stride + o;
+            Num<T>::store(dst, sum.x * factor);
+            Num<T>::store(dst + 1, sum.y * factor);
+            Num<T>::store(dst + 2, sum.z * factor);
+            Num<T>::store(dst + 3, sum.w * factor);
         }
-        Num<T>::store(out + (size_t)row * out_stride + o, value);
+    } else {
+        for (int o = threadIdx.x; o < outputs; o += blockDim.x) {
+            float sum = 0.0f;
+#pragma unroll 8
+            for (int c = 0; c < chunks.total; ++c) sum += __ldcg(parts + (size_t)c * outputs + o);
+            float value = sum * out_scale;
+            if (gate_in != nullptr) {
+                const float z = Num<T>::load(gate_in + (size_t)row * gate_stride + o / value_dim);
+                value *= 1.0f / (1.0f + expf(-z));
+            }
+            Num<T>::store(out + (size_t)row * out_stride + o, value);
+        }
     }
     if (threadIdx.x == 0) tickets[seq] = 0;  // as the next call expects it
 }
@@ -456,7 +511,7 @@ MB_EXPORT size_t mb_talking_decode_chunks(int most_positions, int window, int ke
 MB_EXPORT size_t mb_talking_decode_scratch_floats(int sequences, int heads, int value_dim, int most_positions, int window,
                                                   int keep_first) {
     const size_t chunks = mb_talking_decode_chunks(most_positions, window, keep_first);
-    return (size_t)sequences * chunks * ((size_t)heads * (kChunk + 2) + (size_t)heads * value_dim);
+    return (size_t)sequences * chunks * ((size_t)heads * (kChunk + 2) + (size_t)heads * value_dim) + 4;
 }
 
 MB_EXPORT int mb_talking_attention_decode(const void* q, int q_stride, void* out, int out_stride, int dtype, const void* k_pool,
@@ -476,7 +531,7 @@ MB_EXPORT int mb_talking_attention_decode(const void* q, int q_stride, void* out
     const int max_chunks = (int)mb_talking_decode_chunks(most_positions, window, keep_first);
     float* scores = scratch;
     float* stats = scores + (size_t)sequences * heads * max_chunks * kChunk;
-    float* partial = stats + (size_t)sequences * heads * max_chunks * 2;
+    float* partial = stats + ((size_t)sequences * heads * max_chunks * 2 + 3) / 4 * 4;  // read 16 bytes at a time
     const dim3 grid(max_chunks, sequences);
     const size_t q_bytes = sizeof(float) * (size_t)heads * head_dim;
     const size_t smem = sizeof(float) * (2 * (size_t)heads * kChunk + 2 * heads + (size_t)heads * heads);
