@@ -6,11 +6,11 @@
 // because the weights of a key are mixed across heads after the softmax: w'_h(i, j) = sum_g talk[h, g]
 // w_g(i, j) needs every head's normalised weight.  The visible keys are walked twice in chunks of 32:
 //   walk 1: S_g = Q_g K_c^T per warp, running maximum and sum of every row;
-//   walk 2: S_g again, w_g = exp(S_g - max_g) / sum_g in float, handed to the other warps through shared
-//           memory in the layout of the accumulator registers (16 bytes a lane, so nobody meets in a bank); each
-//           warp mixes its own head's weights from all heads' in float, splits them into two bfloat16
-//           numbers (w' = hi + lo, which keeps about 16 bits of the float weight) and adds
-//           hi . V_c + lo . V_c into its output accumulator.
+//   walk 2: S_g again, w_g = exp(S_g - max_g) / sum_g in float, put side by side with the other heads' in shared
+//           memory; the mixing is itself a product, talk [heads x heads] times weights [heads x 512 elements of the
+//           chunk], shared out over the warps with both factors as two bfloat16 numbers each (hi + lo, about 16
+//           bits of the float value; float accumulation); each warp then takes its own head's mixed weights back,
+//           splits them the same way and adds hi . V_c + lo . V_c into its output accumulator.
 // Keys and values of a chunk are copied to shared memory once per block for all key/value heads, the next
 // chunk's (cp.async, two stages) while the current one is worked on.
 // Scores, weights, the mixing and every sum are float; only the operands of the products are bfloat16.
@@ -36,6 +36,7 @@ constexpr int kKRow = D * 2 + 16;        // padded shared-memory rows: ldmatrix 
 constexpr int kVRow = DV * 2 + 16;
 constexpr int kThreads = 32 * H;
 constexpr int kWeightFloats = 16 * 32;   // one head's weights of a chunk: [register][lane]
+constexpr int kWeightRow = kWeightFloats + 4;  // padded: four heads' values of one element lie in four different banks
 
 using bf16 = __nv_bfloat16;
 
@@ -153,8 +154,9 @@ talking_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __re
     unsigned char* q_smem = smem;                                            // [H][16][kKRow]
     unsigned char* k_smem = q_smem + (size_t)H * kRows * kKRow;             // two stages of [kv_heads][32][kKRow]
     unsigned char* v_smem = k_smem + 2 * (size_t)kv_heads * kKeys * kKRow;  // two stages of [kv_heads][32][kVRow]
-    float* w_smem = reinterpret_cast<float*>(v_smem + 2 * (size_t)kv_heads * kKeys * kVRow);  // [H][16][32]
-    float* talk_smem = w_smem + H * kWeightFloats;                          // [H][H]
+    float* w_smem = reinterpret_cast<float*>(v_smem + 2 * (size_t)kv_heads * kKeys * kVRow);  // [16][kWeightRow]: the weights
+    float* m_smem = w_smem + 16 * kWeightRow;                               // [16][kWeightRow]: the mixed weights
+    float* talk_smem = m_smem + 16 * kWeightRow;                            // [H][H]
 
     // queries: a row beyond the step's tokens repeats the last one (it is computed and not stored)
     for (int i = threadIdx.x; i < H * kRows * (D / 8); i += kThreads) {
@@ -163,12 +165,25 @@ talking_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __re
         *reinterpret_cast<uint4*>(q_smem + (size_t)(h * kRows + row) * kKRow + piece * 16) =
             *reinterpret_cast<const uint4*>(q + (size_t)(q_begin + t0 + source) * q_stride + h * D + piece * 8);
     }
-    if (talk != nullptr)
+    if (talk != nullptr) {
         for (int i = threadIdx.x; i < H * H; i += kThreads) talk_smem[i] = talk[i];
+        for (int i = threadIdx.x + H * kWeightRow; i < 16 * kWeightRow; i += kThreads) w_smem[i] = 0.0f;  // heads that are not there
+    }
     __syncthreads();
-    float mix[H];
+    // the mixing matrix as the 16 x 16 left operand of a product (rows and columns beyond the heads are zero), hi + lo
+    uint32_t talk_hi[4] = {0u, 0u, 0u, 0u}, talk_lo[4] = {0u, 0u, 0u, 0u};
+    if (talk != nullptr) {
 #pragma unroll
-    for (int g = 0; g < H; ++g) mix[g] = talk != nullptr ? talk_smem[head * H + g] : (g == head ? 1.0f : 0.0f);
+        for (int j = 0; j < 4; ++j) {
+            const int row = group_id + 8 * (j & 1), column = 2 * tid4 + 8 * (j >> 1);
+            const float a = (row < H && column < H) ? talk_smem[row * H + column] : 0.0f;
+            const float b = (row < H && column + 1 < H) ? talk_smem[row * H + column + 1] : 0.0f;
+            const __nv_bfloat162 top = __floats2bfloat162_rn(a, b);
+            const __nv_bfloat162 rest = __floats2bfloat162_rn(a - __low2float(top), b - __high2float(top));
+            talk_hi[j] = *reinterpret_cast<const uint32_t*>(&top);
+            talk_lo[j] = *reinterpret_cast<const uint32_t*>(&rest);
+        }
+    }
 
     int row_pos[2], row_first[2];
 #pragma unroll
@@ -273,24 +288,36 @@ talking_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __re
                     s[nt][i] = seen ? exp2f(s[nt][i] * scale_log2 - run_max[r]) * inv_sum[r] : 0.0f;
                 }
             if (talk != nullptr) {
-                float4* shared_weights = reinterpret_cast<float4*>(w_smem);  // [head][accumulator][lane]: 16 bytes a lane
+                // every head's weights of the chunk side by side: w_smem[head][element], element = (accumulator, lane)
 #pragma unroll
                 for (int nt = 0; nt < 4; ++nt)
-                    shared_weights[(head * 4 + nt) * 32 + lane] = make_float4(s[nt][0], s[nt][1], s[nt][2], s[nt][3]);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) w_smem[head * kWeightRow + (nt * 4 + i) * 32 + lane] = s[nt][i];
+                __syncthreads();
+                // mixed[h][element] = sum_g talk[h][g] w[g][element] as products of 16 x 16 by 16 x 8 elements, the
+                // elements shared out over the warps; talk and the weights each as hi + lo (lo x lo is left out)
+                for (int tile = head; tile < kWeightFloats / 8; tile += H) {
+                    const float* column = w_smem + tile * 8 + group_id;
+                    const float x0 = column[(2 * tid4) * kWeightRow], x1 = column[(2 * tid4 + 1) * kWeightRow];
+                    const float x2 = column[(2 * tid4 + 8) * kWeightRow], x3 = column[(2 * tid4 + 9) * kWeightRow];
+                    const __nv_bfloat162 top0 = __floats2bfloat162_rn(x0, x1), top1 = __floats2bfloat162_rn(x2, x3);
+                    const __nv_bfloat162 rest0 = __floats2bfloat162_rn(x0 - __low2float(top0), x1 - __high2float(top0));
+                    const __nv_bfloat162 rest1 = __floats2bfloat162_rn(x2 - __low2float(top1), x3 - __high2float(top1));
+                    const uint32_t b_hi0 = *reinterpret_cast<const uint32_t*>(&top0), b_hi1 = *reinterpret_cast<const uint32_t*>(&top1);
+                    const uint32_t b_lo0 = *reinterpret_cast<const uint32_t*>(&rest0), b_lo1 = *reinterpret_cast<const uint32_t*>(&rest1);
+                    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    mma_bf16(c, talk_lo, b_hi0, b_hi1);
+                    mma_bf16(c, talk_hi, b_lo0, b_lo1);
+                    mma_bf16(c, talk_hi, b_hi0, b_hi1);
+                    float* mixed = m_smem + tile * 8 + 2 * tid4;
+                    if (group_id < H) *reinterpret_cast<float2*>(mixed + group_id * kWeightRow) = make_float2(c[0], c[1]);
+                    if (group_id + 8 < H) *reinterpret_cast<float2*>(mixed + (group_id + 8) * kWeightRow) = make_float2(c[2], c[3]);
+                }
                 __syncthreads();
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt) {
-                    float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-                    for (int g = 0; g < H; ++g) {
-                        const float4 w = shared_weights[(g * 4 + nt) * 32 + lane];
-                        sum.x = fmaf(mix[g], w.x, sum.x);
-                        sum.y = fmaf(mix[g], w.y, sum.y);
-                        sum.z = fmaf(mix[g], w.z, sum.z);
-                        sum.w = fmaf(mix[g], w.w, sum.w);
-                    }
-                    s[nt][0] = sum.x, s[nt][1] = sum.y, s[nt][2] = sum.z, s[nt][3] = sum.w;
-                }
+                    for (int i = 0; i < 4; ++i) s[nt][i] = m_smem[head * kWeightRow + (nt * 4 + i) * 32 + lane];
             }
 #pragma unroll
             for (int part = 0; part < 2; ++part) {
@@ -340,7 +367,7 @@ talking_attention_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __re
 using namespace mb;
 
 static size_t block_bytes(int kv_heads) {
-    return (size_t)H * kRows * kKRow + 2 * (size_t)kv_heads * kKeys * (kKRow + kVRow) + sizeof(float) * ((size_t)H * kWeightFloats + H * H);
+    return (size_t)H * kRows * kKRow + 2 * (size_t)kv_heads * kKeys * (kKRow + kVRow) + sizeof(float) * (2 * 16 * (size_t)kWeightRow + H * H);
 }
 
 MB_EXPORT size_t mb_talking_attention_tc_block_bytes(int kv_heads) { return block_bytes(kv_heads); }

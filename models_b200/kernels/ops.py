@@ -401,7 +401,7 @@ def talking_attention_tc_takes(q: torch.Tensor, out: torch.Tensor, k_pool: torch
         return False
     if q.stride(0) % 8 or out.stride(0) % 2 or q.data_ptr() % 16 or out.data_ptr() % 4 or k_pool.data_ptr() % 16 or v_pool.data_ptr() % 16:
         return False
-    block = (heads * 16 * (2 * head_dim + 16) + 2 * kv_heads * 32 * (2 * head_dim + 2 * value_dim + 32) + 4 * (heads * 512 + heads * heads))
+    block = (heads * 16 * (2 * head_dim + 16) + 2 * kv_heads * 32 * (2 * head_dim + 2 * value_dim + 32) + 4 * (2 * 16 * 516 + heads * heads))
     return block <= 227 * 1024
 
 
