@@ -49,8 +49,9 @@ __device__ __forceinline__ float dot_row(const float* __restrict__ q_shared, con
         for (int d = 0; d < head_dim; d += 8) {
             float kv[8];
             load8(k_row + d, kv);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) sum = fmaf(q_shared[d + i], kv[i], sum);
+            const float4 qa = *reinterpret_cast<const float4*>(q_shared + d), qb = *reinterpret_cast<const float4*>(q_shared + d + 4);
+            sum = fmaf(qa.x, kv[0], sum), sum = fmaf(qa.y, kv[1], sum), sum = fmaf(qa.z, kv[2], sum), sum = fmaf(qa.w, kv[3], sum);
+            sum = fmaf(qb.x, kv[4], sum), sum = fmaf(qb.y, kv[5], sum), sum = fmaf(qb.z, kv[6], sum), sum = fmaf(qb.w, kv[7], sum);
         }
     } else {
         for (int d = 0; d < head_dim; ++d) sum = fmaf(q_shared[d], Num<T>::load(k_row + d), sum);
@@ -119,7 +120,7 @@ __global__ void __launch_bounds__(kMaxThreads) talking_attention_rows_kernel(
     float out_scale) {
     grid_launch_dependents();
     grid_dependency_wait();
-    extern __shared__ float shared[];
+    extern __shared__ __align__(16) float shared[];
     const int seq = blockIdx.y;
     const int q_begin = cu_q[seq];
     const int q_len = cu_q[seq + 1] - q_begin;
@@ -284,7 +285,7 @@ __global__ void __launch_bounds__(kMaxThreads) talking_decode_scores_kernel(
     int max_chunks, int heads, int kv_heads, int head_dim, int page_size, int window, int keep_first, float scale) {
     grid_launch_dependents();
     grid_dependency_wait();
-    extern __shared__ float q_shared[];  // heads * head_dim
+    extern __shared__ __align__(16) float q_shared[];  // heads * head_dim
     const int seq = blockIdx.y, index = blockIdx.x;
     const DecodeChunks chunks(kv_lens[seq], window, keep_first);
     if (index >= chunks.total) return;
@@ -325,7 +326,7 @@ __global__ void __launch_bounds__(kMaxThreads) talking_decode_values_kernel(
     int keep_first, float out_scale) {
     grid_launch_dependents();
     grid_dependency_wait();
-    extern __shared__ float shared[];
+    extern __shared__ __align__(16) float shared[];
     __shared__ int last_block;
     const int seq = blockIdx.y, index = blockIdx.x;
     const DecodeChunks chunks(kv_lens[seq], window, keep_first);

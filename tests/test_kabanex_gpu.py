@@ -80,11 +80,11 @@ def _rounded(t, dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("tokens,window,keep_first,target", [
-    (200, 40, 4, 160),   # the oldest key of the window
-    (200, 40, 4, 159),   # the first key outside it
-    (200, 40, 4, 3),     # the last kept first position
-    (200, 40, 4, 4),     # the first position that is not kept
-    (200, 40, 0, 0),     # nothing kept: position 0 is gone
+    (200, 45, 6, 155),   # the oldest key of the window
+    (200, 45, 6, 154),   # the first key outside it
+    (200, 45, 6, 5),     # the last kept first position
+    (200, 45, 6, 6),     # the first position that is not kept
+    (200, 45, 0, 0),     # nothing kept: position 0 is gone
     (200, 70, 2, 130),   # window longer than a page: its oldest key
     (200, 70, 2, 129),
     (130, 3, 9, 8),      # more kept positions than the window is long
@@ -127,7 +127,7 @@ def test_one_key_decides_the_attention(cuda_device, tokens, window, keep_first, 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim,page", [(1, 1, 8, 8, 32), (6, 2, 20, 12, 64), (3, 3, 40, 72, 128), (16, 4, 64, 128, 64),
-                                                          (1, 1, 16, 16, 32), (6, 3, 96, 160, 64), (8, 8, 32, 48, 128), (12, 2, 48, 64, 64)])
+                                                          (1, 1, 16, 16, 32), (6, 2, 80, 160, 64), (8, 8, 32, 48, 128), (12, 2, 48, 64, 64)])
 def test_attention_sizes_mixing_gate_and_scale(cuda_device, heads, kv_heads, dim, vdim, page, dtype):
     g = torch.Generator().manual_seed(heads * 100 + dim)
     T = 150
