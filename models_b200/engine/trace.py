@@ -86,13 +86,18 @@ def main(argv=None) -> int:
     parser.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     parser.add_argument("--out", required=True, help="folder for <step>.f32 files")
     parser.add_argument("--max-tokens", required=True, type=int,
-                        help="most tokens live requests hold at any time, each rounded up to a multiple of 64")
+                        help="most tokens live requests hold at any time (the partly filled last cache page of every "
+                             "request comes on top and need not be counted)")
     parser.add_argument("--graphs", default="on", choices=["on", "off"],
                         help="replay captured steps as generation does (default), or launch every kernel of every step")
     args = parser.parse_args(argv)
     if args.max_tokens <= 0:
         parser.error("--max-tokens must be positive")
-    engine = engine_from_folder(args.model, args.dtype, args.max_tokens)
+    # A request holds whole cache pages, so each live request may hold up to a page less one position more than its
+    # tokens; there are at most as many live requests as tokens, and room for 256 such pages is cheap.
+    from ..cache.kv_cache import PAGE_SIZE
+
+    engine = engine_from_folder(args.model, args.dtype, args.max_tokens + PAGE_SIZE * min(args.max_tokens, 256))
     if args.graphs == "on":
         # any number of live requests the cache has slots for, of any length it has pages for; captures
         # are made when a batch size and a class of lengths first come up
