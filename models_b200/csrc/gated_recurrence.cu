@@ -20,12 +20,13 @@ namespace mb {
 
 constexpr int kBlockThreads = 1024;  // channels of a block times runs of a block, at most
 constexpr int kMaxChunks = 128;
+constexpr int kKeep = 16;  // tokens of a run whose gates and candidates stay in registers between the walks
 
 __device__ __forceinline__ float sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
 
 // grid (ceil(width / channels), sequences); block (channels, chunks) with channels * chunks <= 1024.
 template <typename T>
-__global__ void mingru_scan_kernel(const T* __restrict__ zin, const T* __restrict__ xin, const T* __restrict__ gin,
+__global__ void __launch_bounds__(kBlockThreads) mingru_scan_kernel(const T* __restrict__ zin, const T* __restrict__ xin, const T* __restrict__ gin,
                                    int in_stride, const float* __restrict__ z_bias, const float* __restrict__ x_bias,
                                    float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu_q,
                                    int width, T* __restrict__ out, int out_stride, float out_scale) {
@@ -44,7 +45,61 @@ __global__ void mingru_scan_kernel(const T* __restrict__ zin, const T* __restric
     const int t0 = min(chunk * per, count), t1 = min(t0 + per, count);
     const float bz = live ? z_bias[channel] : 0.0f, bx = live ? x_bias[channel] : 0.0f;
 
-    // Loads do not depend on the recurrence: eight tokens' inputs are asked for before the first is used.
+    if (chunks > 1 && per <= kKeep) {
+        // Short runs (the usual case: the launcher cuts a prompt into runs of about 16 tokens): every input of the
+        // run is asked for at once, and the gates and candidates of the first walk stay in registers for the
+        // second, which then reads only the output gates.  A token beyond the run has z = 0: it changes nothing.
+        float zk[kKeep], ck[kKeep];
+        if (live) {
+#pragma unroll
+            for (int half = 0; half < kKeep; half += kKeep / 2) {  // (eight tokens' loads at a time: registers)
+                float zr[kKeep / 2], xr[kKeep / 2];
+#pragma unroll
+                for (int u = 0; u < kKeep / 2; ++u) {
+                    const size_t at = (size_t)(first + min(t0 + half + u, count - 1)) * in_stride + channel;
+                    zr[u] = Num<T>::load(zin + at);
+                    xr[u] = Num<T>::load(xin + at);
+                }
+#pragma unroll
+                for (int u = 0; u < kKeep / 2; ++u) {
+                    const float x = xr[u] + bx;
+                    zk[half + u] = t0 + half + u < t1 ? sigmoid(zr[u] + bz) : 0.0f;
+                    ck[half + u] = x >= 0.0f ? x + 0.5f : sigmoid(x);
+                }
+            }
+        }
+        float a = 1.0f, b = 0.0f;
+        if (live) {
+#pragma unroll
+            for (int u = 0; u < kKeep; ++u) {
+                a *= 1.0f - zk[u];
+                b = (1.0f - zk[u]) * b + zk[u] * ck[u];
+            }
+        }
+        a_of[chunk * blockDim.x + threadIdx.x] = a;
+        b_of[chunk * blockDim.x + threadIdx.x] = b;
+        __syncthreads();
+        if (!live) return;
+        float* stored = state + (size_t)slots[seq] * width + channel;
+        float s = *stored;
+        for (int before = 0; before < chunk; ++before) s = a_of[before * blockDim.x + threadIdx.x] * s + b_of[before * blockDim.x + threadIdx.x];
+#pragma unroll
+        for (int half = 0; half < kKeep; half += kKeep / 2) {
+            float gr[kKeep / 2];
+#pragma unroll
+            for (int u = 0; u < kKeep / 2; ++u)
+                gr[u] = Num<T>::load(gin + (size_t)(first + min(t0 + half + u, count - 1)) * in_stride + channel);
+#pragma unroll
+            for (int u = 0; u < kKeep / 2; ++u) {
+                s = (1.0f - zk[half + u]) * s + zk[half + u] * ck[half + u];
+                if (t0 + half + u < t1)
+                    Num<T>::store(out + (size_t)(first + t0 + half + u) * out_stride + channel, out_scale * s * (gr[u] * sigmoid(gr[u])));
+            }
+        }
+        if (chunk == chunks - 1) *stored = s;
+        return;
+    }
+    // Longer runs: loads do not depend on the recurrence, so eight tokens' inputs are asked for before the first is used.
     constexpr int kAhead = 8;
     if (chunks > 1) {
         float a = 1.0f, b = 0.0f;

@@ -173,17 +173,18 @@ def test_rotation_of_part_of_a_head_and_the_cache_write(cuda_device, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_min_gru_scan_ragged_chunked_and_carried(cuda_device, dtype):
+@pytest.mark.parametrize("long_lengths", [[1, 9, 300, 77], [2500, 3, 340, 40]])  # runs of up to 16 tokens; of 20
+def test_min_gru_scan_ragged_chunked_and_carried(cuda_device, dtype, long_lengths):
     """Sequences of 1, 9, 300 and 77 new tokens in one call (the long ones are walked in many runs at once), the
     state carried into a second call, a row stride wider than the state, a scale, and gates that nearly freeze
     the state for a while, so that a start lost between runs would show at the end."""
     from models_b200.kernels import ops
 
     g = torch.Generator().manual_seed(9)
-    R, lengths = 45, [1, 9, 300, 77]
+    R, lengths = 45, long_lengths
     total = sum(lengths)
     wide = torch.randn((total, 3 * R + 11), generator=g, dtype=F) * 2.0
-    wide[40:330, :R] -= 9.0  # z ~ 1e-4: the state barely moves over hundreds of tokens
+    wide[40:330, :R] -= 9.0  # z ~ 1e-4: the state barely moves over hundreds of tokens (they lie in the longest sequence)
     z_bias, x_bias = torch.randn(R, generator=g, dtype=F), torch.randn(R, generator=g, dtype=F)
     wide = _rounded(wide, dtype)
     dev = wide.to(dtype).to(cuda_device)
