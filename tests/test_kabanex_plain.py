@@ -122,3 +122,29 @@ def test_a_window_group_keeps_the_pages_of_the_first_positions():
     cache.release(slot)
     cache.check()
     assert cache.groups[0].pages.held == 0
+
+
+def test_random_model_folder_loads_by_name_and_reports_what_is_wrong(tmp_path):
+    """The random-weights mode writes a Kabanex folder that the loader reads back tensor by tensor; a folder whose
+    talk matrix has another head count is refused with the tensor's name."""
+    import json
+
+    from models_b200.config import load_config
+    from models_b200.engine.model import parameter_requests
+    from models_b200.weights import WeightsError, load_tensors
+    from tiny_kabanex import make_folder
+
+    folder = make_folder(KBX["B"], 5, tmp_path)
+    config = load_config(folder)
+    requests = parameter_requests(config.model_spec())
+    tensors = load_tensors(folder, requests)
+    assert set(tensors) == set(requests)
+    assert tensors["l1.mix.left.talk"].shape == (4, 4) and tensors["l1.mix.right.z.b"].dtype == torch.bfloat16
+    assert "l0.mlp.up" not in tensors and "l1.mlp.up" in tensors  # the first layer has no feed-forward
+    logits = pk.forward(*pk.read_model_folder(folder), [1, 2, 3, 4, 5])
+    assert logits.shape == (5, KBX["B"]["vocab"]) and bool(torch.isfinite(logits).all())
+    raw = json.loads((folder / "config.json").read_text())
+    raw["layers"][1]["mixer"]["left"]["heads"] = 8
+    (folder / "config.json").write_text(json.dumps(raw))
+    with pytest.raises(WeightsError, match="l1.mix.left.talk"):
+        load_tensors(folder, parameter_requests(load_config(folder).model_spec()))
