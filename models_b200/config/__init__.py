@@ -1,5 +1,6 @@
 from .kabanex import KabanexConfig
 from .llama import ConfigError, LlamaConfig, RopeScalingConfig
+from .lovurax import LovuraxConfig
 from .registry import (
     config_from_dict,
     known_architectures,
@@ -13,15 +14,19 @@ from .specs import (
     DenseFeedForwardSpec,
     EmbeddingSpec,
     GatedFeedForwardSpec,
+    GatedResidualBlockSpec,
     HeadSpec,
+    LatentAttentionSpec,
     LayerNormSpec,
     MinGruSpec,
     ModelSpec,
     NormSpec,
     ParallelBlockSpec,
+    RetentionSpec,
     RopeScalingSpec,
     RopeSpec,
     ScheduleEntry,
     SideBySideSpec,
+    SigmoidAttentionSpec,
     TalkingAttentionSpec,
 )

@@ -13,6 +13,7 @@ from typing import Any, Callable, Dict, Mapping
 
 from .kabanex import ARCHITECTURE as KABANEX, KabanexConfig
 from .llama import ConfigError, LlamaConfig
+from .lovurax import ARCHITECTURE as LOVURAX, LovuraxConfig
 
 # name -> callable(raw config.json dict) -> object with .model_spec()
 _ARCHITECTURES: Dict[str, Callable[[Mapping[str, Any]], Any]] = {}
@@ -64,3 +65,4 @@ def load_config(folder):
 
 register_architecture("LlamaForCausalLM", LlamaConfig.from_dict)
 register_architecture(KABANEX, KabanexConfig.from_dict)
+register_architecture(LOVURAX, LovuraxConfig.from_dict)

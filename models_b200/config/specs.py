@@ -129,7 +129,8 @@ class SideBySideSpec:
 
 @dataclass(frozen=True)
 class DenseFeedForwardSpec:
-    """down(act(up(x))), no gate.  activation: a name of the activation table ("relu2": relu squared)."""
+    """down(act(up(x))), no gate.  activation: a name of the activation table ("relu2": relu squared; "xielu": a
+    quadratic above zero and an exponential below it whose two shape numbers are a tensor, `weights["act"]`)."""
 
     hidden_size: int
     intermediate_size: int
@@ -244,3 +245,83 @@ class ModelSpec:
                 if self.schedule[entry.cache_from].cache_from is not None:
                     raise ValueError(
                         f"schedule[{index}] reads the cache of run {entry.cache_from}, which owns none")
+
+
+@dataclass(frozen=True)
+class SigmoidAttentionSpec:
+    """Causal grouped-query attention whose weights are sigmoids, not a softmax: key j <= i gets
+    sigmoid(scale * q_i.k_j - slope_h * (i - j) + bias_h) and the weights are not normalised over keys.
+    slope_h = 2^(-slope_exponent * (h + 1) / heads) (`slope_exponent` 0: no distance term).  `qk_norm`: queries and
+    keys pass an RMS norm per head (eps `eps`, one gain shared by the heads) before anything else.
+    `temperature_coef` c != 0: the query at position p is multiplied by 1 + c * ln(floor((p + 1) / temperature_every) + 1).
+    `head_bias`: bias_h is a tensor of one number per head (else 0).  `gated`: the heads side by side are multiplied
+    element by element by sigmoid(gate . xn) before the output matrix.  There is no rotation."""
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    eps: float
+    qk_norm: bool
+    temperature_coef: float
+    temperature_every: int
+    slope_exponent: float
+    head_bias: bool
+    gated: bool
+    weights: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+    kind: str = "sigmoid_attention"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Causal softmax attention whose keys and values are expanded from ONE cached row per position:
+    c = rmsnorm(down . xn) of `latent_dim` numbers (gain, eps `eps`); head h has k = up_k[h] . c (`head_dim`) and
+    v = up_v[h] . c (`value_dim`); score = scale * q.k; no positions enter.  `gated`: head h's result is multiplied
+    by sigmoid(gate_h . xn), one number per head and token."""
+
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    value_dim: int
+    latent_dim: int
+    scale: float
+    eps: float
+    gated: bool
+    weights: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class RetentionSpec:
+    """Linear attention with a fixed decay per head and no normalisation over keys: per head a float32 state
+    S [head_dim, value_dim] that starts at zero, S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t.  Queries and keys
+    are rotated (`position`, or None), keys then multiplied by `key_scale`; every head's o_t is divided by its root
+    mean square (eps `eps`, no gain), the heads side by side are multiplied by silu(gate . xn), then the output matrix."""
+
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    value_dim: int
+    decay: Tuple[float, ...]
+    key_scale: float
+    eps: float
+    position: Optional[RopeSpec]
+    weights: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+    kind: str = "retention"
+
+
+@dataclass(frozen=True)
+class GatedResidualBlockSpec:
+    """A pre-norm layer whose sublayer results pass a gate on their way into the stream:
+    h = mixer_norm(x); x += sigmoid(Gm . h + bm) * mixer(h); then, if the layer has a feed-forward,
+    h = feed_forward_norm(x); x += sigmoid(Gf . h + bf) * feed_forward(h).  The gates are [width, width] matrices
+    with a bias, named in `weights` (mixer_gate, mixer_gate_bias, feed_forward_gate, feed_forward_gate_bias)."""
+
+    mixer: object
+    feed_forward: Optional[object]
+    mixer_norm: object
+    feed_forward_norm: Optional[object]
+    weights: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+    kind: str = "prenorm_gated"

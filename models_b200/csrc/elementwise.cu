@@ -397,6 +397,52 @@ __global__ void activate_kernel(const T* __restrict__ src, int src_stride, T* __
     }
 }
 
+// xIELU: for z > 0, a_pos z^2 + z/2; for z <= 0, a_neg (exp(z) - 1 - z) + z/2, with a_pos = softplus(p) and
+// a_neg = 1/2 + softplus(q) of the layer's two shape numbers (computed once, on the host, when they are loaded).
+__device__ __forceinline__ float xielu(float z, float a_pos, float a_neg) {
+    return z > 0.0f ? fmaf(a_pos * z, z, 0.5f * z) : fmaf(a_neg, expm1f(z) - z, 0.5f * z);
+}
+
+template <typename T>
+__global__ void xielu_kernel(const T* __restrict__ src, int src_stride, T* __restrict__ dst, int dst_stride, int cols,
+                             size_t total, float a_pos, float a_neg, float scale) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / cols, c = i % cols;
+        Num<T>::store(dst + r * dst_stride + c, scale * xielu(Num<T>::load(src + r * src_stride + c), a_pos, a_neg));
+    }
+}
+
+template <typename T>
+__global__ void xielu_vec8_kernel(const T* __restrict__ src, int src_stride, T* __restrict__ dst, int dst_stride, int cols8,
+                                  size_t total8, float a_pos, float a_neg, float scale) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / cols8, c = (i % cols8) * 8;
+        float v[8];
+        load8(src + r * src_stride + c, v);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = scale * xielu(v[k], a_pos, a_neg);
+        store8(dst + r * dst_stride + c, v);
+    }
+}
+
+// x (float residual stream, [rows, width]) += sigmoid(gate + bias) * delta: gate [rows, width] is a column slice of
+// a wider tensor (row stride in elements), bias [width] float, delta [rows, width] contiguous.  All arithmetic float.
+template <typename TG, typename TD>
+__global__ void gated_residual_add_kernel(float* __restrict__ x, const TG* __restrict__ gate, int gate_stride,
+                                          const float* __restrict__ bias, const TD* __restrict__ delta, int width, size_t total) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / width, c = i % width;
+        const float z = Num<TG>::load(gate + r * gate_stride + c) + bias[c];
+        x[i] = fmaf(1.0f / (1.0f + expf(-z)), Num<TD>::load(delta + i), x[i]);
+    }
+}
+
 }  // namespace mb
 
 using namespace mb;
@@ -625,4 +671,50 @@ MB_EXPORT int mb_residual_add(float* x, const void* delta, int delta_dtype, size
     else
         return fail("residual_add: unknown dtype code %d", delta_dtype);
     return check_launch("residual_add");
+}
+
+// dst[r, c] = scale * xielu(src[r, c]) for [rows, cols] column slices with row strides (in elements).
+MB_EXPORT int mb_xielu(const void* src, int src_stride, void* dst, int dst_stride, int dtype, int rows, int cols, float a_pos,
+                       float a_neg, float scale, cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return 0;
+    const size_t total = (size_t)rows * cols;
+    const size_t align = dtype == MB_F32 ? 31 : 15;
+    if (dtype != MB_F32 && dtype != MB_BF16) return fail("xielu: unknown dtype code %d", dtype);
+    if (cols % 8 == 0 && src_stride % 8 == 0 && dst_stride % 8 == 0 && !((uintptr_t)src & align) && !((uintptr_t)dst & align)) {
+        const size_t total8 = total / 8;
+        if (dtype == MB_F32)
+            MB_LAUNCH("elementwise", xielu_vec8_kernel<float>, dim3(grid_for(total8, 256)), dim3(256), 0, stream, true,
+                      (const float*)src, src_stride, (float*)dst, dst_stride, cols / 8, total8, a_pos, a_neg, scale);
+        else
+            MB_LAUNCH("elementwise", xielu_vec8_kernel<__nv_bfloat16>, dim3(grid_for(total8, 256)), dim3(256), 0, stream, true,
+                      (const __nv_bfloat16*)src, src_stride, (__nv_bfloat16*)dst, dst_stride, cols / 8, total8, a_pos, a_neg, scale);
+        return check_launch("xielu");
+    }
+    if (dtype == MB_F32)
+        MB_LAUNCH("elementwise", xielu_kernel<float>, dim3(grid_for(total, 256)), dim3(256), 0, stream, true, (const float*)src,
+                  src_stride, (float*)dst, dst_stride, cols, total, a_pos, a_neg, scale);
+    else
+        MB_LAUNCH("elementwise", xielu_kernel<__nv_bfloat16>, dim3(grid_for(total, 256)), dim3(256), 0, stream, true,
+                  (const __nv_bfloat16*)src, src_stride, (__nv_bfloat16*)dst, dst_stride, cols, total, a_pos, a_neg, scale);
+    return check_launch("xielu");
+}
+
+// x += sigmoid(gate + bias) * delta; gate and delta each float or bfloat16.
+MB_EXPORT int mb_gated_residual_add(float* x, const void* gate, int gate_stride, int gate_dtype, const float* bias,
+                                    const void* delta, int delta_dtype, int rows, int width, cudaStream_t stream) {
+    if (rows <= 0 || width <= 0) return 0;
+    const size_t total = (size_t)rows * width;
+    const dim3 grid(grid_for(total, 256)), block(256);
+    if (gate_dtype == MB_F32 && delta_dtype == MB_F32)
+        MB_LAUNCH("elementwise", gated_residual_add_kernel<float, float>, dim3(grid), dim3(block), 0, stream, true, x,
+                  (const float*)gate, gate_stride, bias, (const float*)delta, width, total);
+    else if (gate_dtype == MB_BF16 && delta_dtype == MB_F32)
+        MB_LAUNCH("elementwise", gated_residual_add_kernel<__nv_bfloat16, float>, dim3(grid), dim3(block), 0, stream, true, x,
+                  (const __nv_bfloat16*)gate, gate_stride, bias, (const float*)delta, width, total);
+    else if (gate_dtype == MB_BF16 && delta_dtype == MB_BF16)
+        MB_LAUNCH("elementwise", gated_residual_add_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(block), 0, stream, true,
+                  x, (const __nv_bfloat16*)gate, gate_stride, bias, (const __nv_bfloat16*)delta, width, total);
+    else
+        return fail("gated_residual_add: gate dtype %d with delta dtype %d is not built", gate_dtype, delta_dtype);
+    return check_launch("gated_residual_add");
 }

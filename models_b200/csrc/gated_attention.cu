@@ -1,0 +1,333 @@
+// Causal attention over a paged cache for mixers whose weights are not (only) a softmax of scaled dot products,
+// in plain float arithmetic; float or bfloat16 storage.
+//
+//   score(i, j) = scale * q_h(i) . k_c(j) - slope_h * (i - j) + bias_h         c = h / (heads / kv_heads)
+//   slope_h = 2^(-slope_exponent * (h + 1) / heads)   (slope_exponent 0: no distance term);  bias absent: 0
+//   weight(i, j), j <= i:  softmax over j of score(i, .)     or     sigmoid(score(i, j)), not normalised over j
+//   out_h(i) = gate * sum_j weight(i, j) v_c(j)
+//   gate: none, sigmoid of one number per (token, head), or sigmoid of one number per output element
+//
+// Keys have head_dim coordinates and values value_dim; the value rows may lie in a pool of their own or be the
+// first value_dim coordinates of the key rows (a cache that keeps one row per position, read as key and as value).
+//
+// Cache layout of one layer: k_pool[page][kv_head][page_size][head_dim], v_pool[page][kv_head][page_size][v_width];
+// block_table[seq][i] is the page that holds positions [i*page_size, (i+1)*page_size) of that sequence.
+//
+// Beside the attention: the kernel that normalises query and key heads (RMS norm with a gain shared by the heads),
+// scales queries by a temperature that grows with the position, and stores keys and values in the cache; and a
+// product with one small matrix per head, out[t, h, :] = W_h in[t, h, :].
+#include "common.cuh"
+
+#include <math_constants.h>
+
+MB_DEFINE_LAST_ERROR()
+
+namespace mb {
+
+constexpr int kGateHead = 1, kGateElement = 2;  // gate kinds (0: no gate)
+
+__device__ __forceinline__ float sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
+
+// grid (tokens); block: a multiple of 32 threads; a warp per head.
+//   q head (in place): q / rms(q) * q_gain * (1 + temp_coef * ln(floor((p + 1) / temp_every) + 1))
+//   k head (into the cache): k / rms(k) * k_gain;  v head (into the cache, if value_dim > 0): as it is.
+// rms(x) = sqrt(mean(x^2) + eps).  A null gain means: that side is not normalised.
+template <typename T>
+__global__ void norm_store_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride,
+                                  const T* __restrict__ v, int v_stride, const int* __restrict__ positions,
+                                  const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps,
+                                  float temp_coef, int temp_every, T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                  const int* __restrict__ slot_mapping, int heads, int kv_heads, int head_dim,
+                                  int value_dim, int page_size) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int token = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int pos = positions[token];
+    const int slot = slot_mapping[token];
+    const size_t page = slot >= 0 ? slot / page_size : 0, offset = slot >= 0 ? slot % page_size : 0;
+    float temperature = 1.0f;
+    if (temp_coef != 0.0f) temperature = 1.0f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.0f);
+    for (int item = warp; item < heads + kv_heads; item += warps) {
+        const bool is_query = item < heads;
+        const int head = is_query ? item : item - heads;
+        const float* gain = is_query ? q_gain : k_gain;
+        T* q_head = q + (size_t)token * q_stride + (size_t)head * head_dim;
+        const T* src = is_query ? q_head : k + (size_t)token * k_stride + (size_t)head * head_dim;
+        if (!is_query && slot < 0) continue;  // a padding row stores nothing
+        T* dst = is_query ? q_head : k_pool + ((page * kv_heads + head) * page_size + offset) * head_dim;
+        float factor = is_query ? temperature : 1.0f;
+        if (gain != nullptr) {
+            float ssq = 0.0f;
+            for (int d = lane; d < head_dim; d += 32) {
+                const float x = Num<T>::load(src + d);
+                ssq = fmaf(x, x, ssq);
+            }
+            ssq = warp_sum(ssq);
+            factor *= 1.0f / sqrtf(ssq / (float)head_dim + eps);
+        }
+        for (int d = lane; d < head_dim; d += 32) {
+            float x = Num<T>::load(src + d);
+            if (gain != nullptr) x *= gain[d];
+            Num<T>::store(dst + d, x * factor);
+        }
+    }
+    if (slot < 0 || value_dim <= 0) return;
+    const T* v_row = v + (size_t)token * v_stride;
+    for (int item = threadIdx.x; item < kv_heads * value_dim; item += blockDim.x) {
+        const int head = item / value_dim, d = item % value_dim;
+        v_pool[((page * kv_heads + head) * page_size + offset) * value_dim + d] = v_row[(size_t)head * value_dim + d];
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ float dot_row(const float* __restrict__ q_shared, const T* __restrict__ k_row, int head_dim,
+                                         bool vector_ok) {
+    float sum = 0.0f;
+    if (vector_ok) {
+        for (int d = 0; d < head_dim; d += 8) {
+            float kv[8];
+            load8(k_row + d, kv);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sum = fmaf(q_shared[d + i], kv[i], sum);
+        }
+    } else {
+        for (int d = 0; d < head_dim; ++d) sum = fmaf(q_shared[d], Num<T>::load(k_row + d), sum);
+    }
+    return sum;
+}
+
+// One warp per (token, head).  grid (ceil(max_q_len / warps), heads, sequences); block warps * 32.
+// kAcc: value coordinates a lane accumulates (value_dim <= 32 * kAcc).  The softmax is the running form: a running
+// maximum, partial sums rescaled when it grows.
+template <typename T, int kWarps, int kAcc, bool kSoftmax>
+__global__ void __launch_bounds__(kWarps * 32)
+gated_attention_rows_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
+                            const T* __restrict__ k_pool, const T* __restrict__ v_pool, int v_width,
+                            const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
+                            const int* __restrict__ kv_lens, const float* __restrict__ head_bias,
+                            const T* __restrict__ gate, int gate_stride, int gate_kind, int heads, int kv_heads,
+                            int head_dim, int value_dim, int page_size, float scale, float slope_exponent) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    extern __shared__ float q_shared_all[];  // kWarps * head_dim floats
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seq = blockIdx.z, head = blockIdx.y;
+    const int q_begin = cu_q[seq];
+    const int q_len = cu_q[seq + 1] - q_begin;
+    const int j = blockIdx.x * kWarps + warp;
+    if (j >= q_len) return;  // no block-wide barrier below, so a warp may leave alone
+    const int row = q_begin + j;
+    const int pos = kv_lens[seq] - q_len + j;
+    const int kv_head = head / (heads / kv_heads);
+    const bool vector_ok = (head_dim % 8) == 0 && (((size_t)k_pool) & (sizeof(T) * 8 - 1)) == 0;
+    const float slope = slope_exponent != 0.0f ? exp2f(-slope_exponent * (float)(head + 1) / (float)heads) : 0.0f;
+    const float bias = head_bias != nullptr ? head_bias[head] : 0.0f;
+
+    float* q_shared = q_shared_all + warp * head_dim;
+    const T* q_row = q + (size_t)row * q_stride + (size_t)head * head_dim;
+    for (int d = lane; d < head_dim; d += 32) q_shared[d] = Num<T>::load(q_row + d);
+    __syncwarp();
+
+    float acc[kAcc];
+#pragma unroll
+    for (int i = 0; i < kAcc; ++i) acc[i] = 0.0f;
+    float running_max = -CUDART_INF_F, running_sum = 0.0f;
+    const int* table = block_table + (size_t)seq * max_blocks;
+
+    for (int chunk = 0; chunk <= pos; chunk += 32) {
+        // page_size is a multiple of 32, so a chunk of 32 positions lies in one page
+        const size_t page = table[chunk / page_size];
+        const size_t base = (page * kv_heads + kv_head) * page_size + (chunk % page_size);
+        const int p = chunk + lane;
+        const bool visible = p <= pos;
+        float score = -CUDART_INF_F;
+        if (visible)
+            score = dot_row<T>(q_shared, k_pool + (base + lane) * head_dim, head_dim, vector_ok) * scale - slope * (float)(pos - p) + bias;
+        float weight;
+        if (kSoftmax) {
+            const float new_max = fmaxf(running_max, warp_max(score));  // finite: every chunk holds a visible key
+            weight = visible ? expf(score - new_max) : 0.0f;
+            const float correction = expf(running_max - new_max);  // exp(-inf) = 0 on the first chunk
+            running_sum = running_sum * correction + warp_sum(weight);
+            running_max = new_max;
+#pragma unroll
+            for (int i = 0; i < kAcc; ++i) acc[i] *= correction;
+        } else {
+            weight = visible ? sigmoid(score) : 0.0f;
+        }
+        const int last = (pos - chunk < 31) ? pos - chunk : 31;
+        for (int jj = 0; jj <= last; ++jj) {
+            const float w = __shfl_sync(0xffffffffu, weight, jj);
+            const T* v_row = v_pool + (base + jj) * v_width;
+#pragma unroll
+            for (int i = 0; i < kAcc; ++i) {
+                const int d = lane + 32 * i;
+                if (d < value_dim) acc[i] = fmaf(w, Num<T>::load(v_row + d), acc[i]);
+            }
+        }
+    }
+    float factor = kSoftmax ? 1.0f / running_sum : 1.0f;
+    if (gate_kind == kGateHead) factor *= sigmoid(Num<T>::load(gate + (size_t)row * gate_stride + head));
+    T* out_row = out + (size_t)row * out_stride + (size_t)head * value_dim;
+#pragma unroll
+    for (int i = 0; i < kAcc; ++i) {
+        const int d = lane + 32 * i;
+        if (d < value_dim) {
+            float value = acc[i] * factor;
+            if (gate_kind == kGateElement)
+                value *= sigmoid(Num<T>::load(gate + (size_t)row * gate_stride + (size_t)head * value_dim + d));
+            Num<T>::store(out_row + d, value);
+        }
+    }
+}
+
+// out[t, h * n_out + n] = gate * sum_k in[t, h * n_in + k] * w[(h * n_out + n) * n_in + k]: one small matrix per head,
+// rows of n_in weights; gate: sigmoid of gate[t, h] when given.  grid (ceil(tokens / kRows), heads); block 128.
+// shared: kRows * n_in floats.
+constexpr int kHeadRows = 16;
+
+template <typename T>
+__global__ void head_linear_kernel(const T* __restrict__ in, int in_stride, const T* __restrict__ w, T* __restrict__ out,
+                                   int out_stride, const T* __restrict__ gate, int gate_stride, int tokens, int n_in, int n_out) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    extern __shared__ float rows_shared[];  // [kHeadRows][n_in]
+    const int head = blockIdx.y, first = blockIdx.x * kHeadRows;
+    const int rows = min(kHeadRows, tokens - first);
+    for (int item = threadIdx.x; item < kHeadRows * n_in; item += blockDim.x) {
+        const int r = item / n_in, k = item % n_in;
+        rows_shared[item] = r < rows ? Num<T>::load(in + (size_t)(first + r) * in_stride + (size_t)head * n_in + k) : 0.0f;
+    }
+    __syncthreads();
+    for (int n = threadIdx.x; n < n_out; n += blockDim.x) {
+        const T* w_row = w + ((size_t)head * n_out + n) * n_in;
+        float acc[kHeadRows];
+#pragma unroll
+        for (int r = 0; r < kHeadRows; ++r) acc[r] = 0.0f;
+        for (int k = 0; k < n_in; ++k) {
+            const float weight = Num<T>::load(w_row + k);
+#pragma unroll
+            for (int r = 0; r < kHeadRows; ++r) acc[r] = fmaf(rows_shared[r * n_in + k], weight, acc[r]);
+        }
+#pragma unroll
+        for (int r = 0; r < kHeadRows; ++r) {
+            if (r < rows) {
+                float value = acc[r];
+                if (gate != nullptr) value *= sigmoid(Num<T>::load(gate + (size_t)(first + r) * gate_stride + head));
+                Num<T>::store(out + (size_t)(first + r) * out_stride + (size_t)head * n_out + n, value);
+            }
+        }
+    }
+}
+
+template <typename T>
+int launch_norm_store(void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, const int* positions,
+                      const float* q_gain, const float* k_gain, float eps, float temp_coef, int temp_every, void* k_pool,
+                      void* v_pool, const int* slot_mapping, int tokens, int heads, int kv_heads, int head_dim, int value_dim,
+                      int page_size, cudaStream_t stream) {
+    MB_LAUNCH("norm_store", norm_store_kernel<T>, dim3(tokens), dim3(128), 0, stream, true, (T*)q, q_stride, (const T*)k,
+              k_stride, (const T*)v, v_stride, positions, q_gain, k_gain, eps, temp_coef, temp_every, (T*)k_pool, (T*)v_pool,
+              slot_mapping, heads, kv_heads, head_dim, value_dim, page_size);
+    return 0;
+}
+
+template <typename T, int kAcc, bool kSoftmax>
+int launch_rows(const void* q, int q_stride, void* out, int out_stride, const void* k_pool, const void* v_pool, int v_width,
+                const int* block_table, int max_blocks, const int* cu_q, const int* kv_lens, const float* head_bias,
+                const void* gate, int gate_stride, int gate_kind, int sequences, int max_q_len, int heads, int kv_heads,
+                int head_dim, int value_dim, int page_size, float scale, float slope_exponent, cudaStream_t stream) {
+    constexpr int kWarps = 4;
+    const dim3 grid((max_q_len + kWarps - 1) / kWarps, heads, sequences);
+    const size_t smem = (size_t)kWarps * head_dim * sizeof(float);
+    MB_LAUNCH("gated_attention_rows", (gated_attention_rows_kernel<T, kWarps, kAcc, kSoftmax>), dim3(grid), dim3(kWarps * 32), smem,
+              stream, true, (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pool, (const T*)v_pool, v_width, block_table,
+              max_blocks, cu_q, kv_lens, head_bias, (const T*)gate, gate_stride, gate_kind, heads, kv_heads, head_dim, value_dim,
+              page_size, scale, slope_exponent);
+    return 0;
+}
+
+template <typename T, bool kSoftmax, typename... Args>
+int pick_rows(int value_dim, Args... args) {
+    if (value_dim <= 128) return launch_rows<T, 4, kSoftmax>(args...);
+    if (value_dim <= 256) return launch_rows<T, 8, kSoftmax>(args...);
+    return launch_rows<T, 16, kSoftmax>(args...);
+}
+
+}  // namespace mb
+
+using namespace mb;
+
+MB_EXPORT int mb_norm_store(void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, int dtype,
+                            const int* positions, const float* q_gain, const float* k_gain, float eps, float temp_coef,
+                            int temp_every, void* k_pool, void* v_pool, const int* slot_mapping, int tokens, int heads,
+                            int kv_heads, int head_dim, int value_dim, int page_size, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (head_dim <= 0 || kv_heads <= 0 || heads < 0 || value_dim < 0 || page_size <= 0)
+        return fail("norm_store: sizes must be positive (heads %d, kv heads %d, head_dim %d, value_dim %d)", heads, kv_heads, head_dim, value_dim);
+    if (temp_every < 1) return fail("norm_store: the temperature's period must be at least 1, got %d", temp_every);
+    int status;
+    if (dtype == MB_F32)
+        status = launch_norm_store<float>(q, q_stride, k, k_stride, v, v_stride, positions, q_gain, k_gain, eps, temp_coef, temp_every,
+                                          k_pool, v_pool, slot_mapping, tokens, heads, kv_heads, head_dim, value_dim, page_size, stream);
+    else if (dtype == MB_BF16)
+        status = launch_norm_store<__nv_bfloat16>(q, q_stride, k, k_stride, v, v_stride, positions, q_gain, k_gain, eps, temp_coef,
+                                                  temp_every, k_pool, v_pool, slot_mapping, tokens, heads, kv_heads, head_dim, value_dim,
+                                                  page_size, stream);
+    else
+        return fail("norm_store: unknown dtype code %d", dtype);
+    return status ? status : check_launch("norm_store");
+}
+
+// q: rows of `heads` heads of head_dim (row stride in elements); out: rows of `heads` heads of value_dim.
+// softmax != 0: softmax weights; 0: sigmoid weights.  gate_kind: 0 none, 1 [tokens, heads], 2 [tokens, heads * value_dim].
+MB_EXPORT int mb_gated_attention_rows(const void* q, int q_stride, void* out, int out_stride, int dtype, const void* k_pool,
+                                      const void* v_pool, int v_width, const int* block_table, int max_blocks, const int* cu_q,
+                                      const int* kv_lens, const float* head_bias, const void* gate, int gate_stride, int gate_kind,
+                                      int sequences, int max_q_len, int heads, int kv_heads, int head_dim, int value_dim,
+                                      int page_size, int softmax, float scale, float slope_exponent, cudaStream_t stream) {
+    if (sequences <= 0 || max_q_len <= 0) return 0;
+    if (head_dim <= 0 || head_dim > 2048) return fail("gated_attention_rows: head_dim %d is outside 1..2048", head_dim);
+    if (value_dim <= 0 || value_dim > 512 || value_dim > v_width)
+        return fail("gated_attention_rows: value_dim %d is outside 1..512 or beyond the value rows of %d", value_dim, v_width);
+    if (kv_heads <= 0 || heads % kv_heads) return fail("gated_attention_rows: %d heads are no multiple of %d kv heads", heads, kv_heads);
+    if (page_size <= 0 || page_size % 32) return fail("gated_attention_rows: page_size %d must be a multiple of 32", page_size);
+    if (sequences > 65535 || heads > 65535) return fail("gated_attention_rows: %d sequences or %d heads exceed the grid limit 65535", sequences, heads);
+    if (gate_kind < 0 || gate_kind > 2 || (gate_kind != 0 && gate == nullptr)) return fail("gated_attention_rows: gate kind %d", gate_kind);
+    int status;
+#define MB_ROWS(T, S)                                                                                                          \
+    pick_rows<T, S>(value_dim, q, q_stride, out, out_stride, k_pool, v_pool, v_width, block_table, max_blocks, cu_q, kv_lens,  \
+                    head_bias, gate, gate_stride, gate_kind, sequences, max_q_len, heads, kv_heads, head_dim, value_dim,       \
+                    page_size, scale, slope_exponent, stream)
+    if (dtype == MB_F32)
+        status = softmax ? MB_ROWS(float, true) : MB_ROWS(float, false);
+    else if (dtype == MB_BF16)
+        status = softmax ? MB_ROWS(__nv_bfloat16, true) : MB_ROWS(__nv_bfloat16, false);
+    else
+        return fail("gated_attention_rows: unknown dtype code %d", dtype);
+#undef MB_ROWS
+    return status ? status : check_launch("gated_attention_rows");
+}
+
+MB_EXPORT int mb_head_linear(const void* in, int in_stride, const void* w, void* out, int out_stride, int dtype, const void* gate,
+                             int gate_stride, int tokens, int heads, int n_in, int n_out, cudaStream_t stream) {
+    if (tokens <= 0 || heads <= 0) return 0;
+    if (n_in <= 0 || n_out <= 0) return fail("head_linear: sizes must be positive, got %d -> %d", n_in, n_out);
+    if (heads > 65535) return fail("head_linear: %d heads exceed the grid limit 65535", heads);
+    const size_t smem = (size_t)kHeadRows * n_in * sizeof(float);
+    if (smem > 200 * 1024) return fail("head_linear: %d inputs per head exceed a block's shared memory", n_in);
+    const dim3 grid((tokens + kHeadRows - 1) / kHeadRows, heads);
+    if (dtype == MB_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(head_linear_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        MB_LAUNCH("head_linear", head_linear_kernel<float>, dim3(grid), dim3(128), smem, stream, true, (const float*)in, in_stride,
+                  (const float*)w, (float*)out, out_stride, (const float*)gate, gate_stride, tokens, n_in, n_out);
+    } else if (dtype == MB_BF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(head_linear_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        MB_LAUNCH("head_linear", head_linear_kernel<__nv_bfloat16>, dim3(grid), dim3(128), smem, stream, true, (const __nv_bfloat16*)in,
+                  in_stride, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)gate, gate_stride, tokens,
+                  n_in, n_out);
+    } else {
+        return fail("head_linear: unknown dtype code %d", dtype);
+    }
+    return check_launch("head_linear");
+}

@@ -1,0 +1,135 @@
+// Retention: linear attention with a fixed decay per head and a float state per sequence and head, over the new
+// tokens of ragged sequences.
+//
+//   q_t, k_t: rotated over their first rotary_dim coordinates (split-half pairs, angles from float tables by the
+//             token's position), k_t then multiplied by key_scale
+//   S_t = decay_h S_(t-1) + k_t v_t^T          S [head_dim, value_dim], float, one per (sequence, head), kept between steps
+//   o_t = S_t^T q_t
+//   y_t = out_scale * o_t / sqrt(mean(o_t^2) + eps) * silu(g_t)          (the mean over the head's value_dim numbers)
+//
+// q, k, v, g are projections of the token (storage type, float or bfloat16); everything after them is float.
+//
+// A block owns one (sequence, head): a thread per value coordinate j keeps column j of S in shared memory
+// ([head_dim][value_dim], so that neighbouring threads touch neighbouring words) and walks the sequence's new tokens
+// in order.  The state is read from the state area when the block starts and written back when it ends.
+#include "common.cuh"
+
+MB_DEFINE_LAST_ERROR()
+
+namespace mb {
+
+// grid (heads, sequences); block: value_dim rounded up to a multiple of 32 (at most 1024).
+// shared: S [head_dim * value_dim], q [2][head_dim], k [2][head_dim], 32 floats for sums.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ g,
+                      int in_stride, const int* __restrict__ positions, const float* __restrict__ cos_table,
+                      const float* __restrict__ sin_table, int rotary_dim, const float* __restrict__ decay, float key_scale,
+                      float eps, float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu_q,
+                      int heads, int head_dim, int value_dim, T* __restrict__ out, int out_stride, float out_scale) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    extern __shared__ __align__(16) float shared[];
+    const int head = blockIdx.x, seq = blockIdx.y;
+    const int first = cu_q[seq];
+    const int count = cu_q[seq + 1] - first;
+    if (count <= 0) return;  // the whole block leaves
+    float* S = shared;
+    float* qk = S + (size_t)head_dim * value_dim;  // [2 buffers][q | k][head_dim]
+    float* sums = qk + 4 * head_dim;
+    const int j = threadIdx.x;
+    const bool live = j < value_dim;
+    const int half = rotary_dim / 2;
+    const float a = decay[head];
+    float* stored = state + ((size_t)slots[seq] * heads + head) * head_dim * value_dim;
+    if (live)
+        for (int d = 0; d < head_dim; ++d) S[d * value_dim + j] = stored[(size_t)d * value_dim + j];
+
+    // rotated query and scaled rotated key of token t into buffer `b`
+    auto stage = [&](int t, int b) {
+        const size_t row = (size_t)(first + t) * in_stride + (size_t)head * head_dim;
+        const int pos = positions[first + t];
+        const float* cos_row = cos_table + (size_t)pos * half;
+        const float* sin_row = sin_table + (size_t)pos * half;
+        for (int item = threadIdx.x; item < 2 * head_dim; item += blockDim.x) {
+            const bool is_key = item >= head_dim;
+            const int d = is_key ? item - head_dim : item;
+            const T* x = (is_key ? k : q) + row;
+            float value;
+            if (d < half)
+                value = Num<T>::load(x + d) * cos_row[d] - Num<T>::load(x + d + half) * sin_row[d];
+            else if (d < rotary_dim)
+                value = Num<T>::load(x + d) * cos_row[d - half] + Num<T>::load(x + d - half) * sin_row[d - half];
+            else
+                value = Num<T>::load(x + d);
+            qk[b * 2 * head_dim + item] = is_key ? value * key_scale : value;
+        }
+    };
+
+    stage(0, 0);
+    __syncthreads();
+    for (int t = 0; t < count; ++t) {
+        const int b = t & 1;
+        if (t + 1 < count) stage(t + 1, b ^ 1);  // the next token's q and k while this one is worked on
+        const float* qs = qk + b * 2 * head_dim;
+        const float* ks = qs + head_dim;
+        float o = 0.0f;
+        if (live) {
+            const float vj = Num<T>::load(v + (size_t)(first + t) * in_stride + (size_t)head * value_dim + j);
+            float* column = S + j;
+#pragma unroll 4
+            for (int d = 0; d < head_dim; ++d) {
+                const float s = fmaf(a, column[d * value_dim], ks[d] * vj);
+                column[d * value_dim] = s;
+                o = fmaf(s, qs[d], o);
+            }
+        }
+        const float ssq = block_sum(o * o, sums);  // (two barriers inside: the other buffer is staged when it returns)
+        if (live) {
+            const float gate = Num<T>::load(g + (size_t)(first + t) * in_stride + (size_t)head * value_dim + j);
+            const float y = o / sqrtf(ssq / (float)value_dim + eps) * (gate / (1.0f + expf(-gate)));
+            Num<T>::store(out + (size_t)(first + t) * out_stride + (size_t)head * value_dim + j, out_scale * y);
+        }
+        __syncthreads();  // nobody still reads buffer b when the next round stages over it
+    }
+    if (live)
+        for (int d = 0; d < head_dim; ++d) stored[(size_t)d * value_dim + j] = S[d * value_dim + j];
+}
+
+}  // namespace mb
+
+using namespace mb;
+
+// q, k: [tokens, >= heads * head_dim]; v, g: [tokens, >= heads * value_dim]; all four column slices of one tensor
+// (one row stride).  state: float [slots, heads, head_dim, value_dim]; slots[sequence] picks the row.
+// rotary_dim 0: no rotation (the tables may then be null).
+MB_EXPORT int mb_retention_scan(const void* q, const void* k, const void* v, const void* g, int in_stride, int dtype,
+                                const int* positions, const float* cos_table, const float* sin_table, int rotary_dim,
+                                const float* decay, float key_scale, float eps, float* state, const int* slots, const int* cu_q,
+                                int sequences, int heads, int head_dim, int value_dim, void* out, int out_stride, float out_scale,
+                                cudaStream_t stream) {
+    if (sequences <= 0 || heads <= 0) return 0;
+    if (head_dim <= 0 || value_dim <= 0 || value_dim > 1024) return fail("retention_scan: head_dim %d, value_dim %d (at most 1024)", head_dim, value_dim);
+    if (rotary_dim < 0 || rotary_dim % 2 || rotary_dim > head_dim) return fail("retention_scan: rotary_dim %d must be even and at most %d", rotary_dim, head_dim);
+    if (rotary_dim > 0 && (cos_table == nullptr || sin_table == nullptr)) return fail("retention_scan: rotation needs its tables");
+    if (sequences > 65535) return fail("retention_scan: %d sequences exceed the grid limit 65535", sequences);
+    const size_t smem = ((size_t)head_dim * value_dim + 4 * head_dim + 32) * sizeof(float);
+    if (smem > 227 * 1024) return fail("retention_scan: a state of %d x %d floats exceeds a block's shared memory", head_dim, value_dim);
+    const dim3 grid(heads, sequences), block((value_dim + 31) / 32 * 32);
+    if (dtype == MB_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(retention_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        MB_LAUNCH("retention_scan", retention_scan_kernel<float>, dim3(grid), dim3(block), smem, stream, true, (const float*)q,
+                  (const float*)k, (const float*)v, (const float*)g, in_stride, positions, cos_table, sin_table, rotary_dim, decay,
+                  key_scale, eps, state, slots, cu_q, heads, head_dim, value_dim, (float*)out, out_stride, out_scale);
+    } else if (dtype == MB_BF16) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(retention_scan_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        MB_LAUNCH("retention_scan", retention_scan_kernel<__nv_bfloat16>, dim3(grid), dim3(block), smem, stream, true,
+                  (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const __nv_bfloat16*)g, in_stride,
+                  positions, cos_table, sin_table, rotary_dim, decay, key_scale, eps, state, slots, cu_q, heads, head_dim, value_dim,
+                  (__nv_bfloat16*)out, out_stride, out_scale);
+    } else {
+        return fail("retention_scan: unknown dtype code %d", dtype);
+    }
+    return check_launch("retention_scan");
+}

@@ -12,6 +12,8 @@ LIBRARIES = [
     ("mb_sampling", ["sampling.cu"], {}),
     ("mb_talking_attention", ["talking_attention.cu"], {}),
     ("mb_gated_recurrence", ["gated_recurrence.cu"], {}),
+    ("mb_gated_attention", ["gated_attention.cu"], {}),
+    ("mb_retention", ["retention.cu"], {}),
     ("mb_random_init", ["random_init.cu"], {}),
     ("mb_skinny_gemm", ["skinny_gemm.cu"], {}),
     ("mb_gemm_tcgen05", ["gemm_tcgen05.cu"], {}),

@@ -307,6 +307,37 @@ def activate(src: torch.Tensor, dst: torch.Tensor, activation: str, scale: float
     return dst
 
 
+def xielu(src: torch.Tensor, dst: torch.Tensor, a_pos: float, a_neg: float, scale: float = 1.0) -> torch.Tensor:
+    """dst = scale * (a_pos z^2 + z/2 where z > 0, a_neg (exp(z) - 1 - z) + z/2 elsewhere), element by element; both may
+    be column slices of wider tensors."""
+    _cuda(src, dst)
+    _columns(src, "src")
+    _columns(dst, "dst")
+    if src.shape != dst.shape or src.dtype != dst.dtype:
+        raise KernelError(f"xielu: {tuple(src.shape)} {src.dtype} does not fit {tuple(dst.shape)} {dst.dtype}")
+    lib = elementwise()
+    _run(lib, lib.mb_xielu(_p(src), src.stride(0), _p(dst), dst.stride(0), _code(src.dtype), src.shape[0], src.shape[1],
+                           ctypes.c_float(a_pos), ctypes.c_float(a_neg), ctypes.c_float(scale), _stream()))
+    return dst
+
+
+def gated_residual_add(x: torch.Tensor, gate: torch.Tensor, bias: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    """x += sigmoid(gate + bias) * delta for the float32 residual stream x [rows, width]; gate [rows, width] may be a
+    column slice, bias is float32 [width], delta contiguous [rows, width]; float arithmetic."""
+    _cuda(x, gate, bias, delta)
+    _columns(gate, "gate")
+    if x.dtype != torch.float32 or not x.is_contiguous() or x.dim() != 2:
+        raise KernelError("gated_residual_add: x must be a contiguous float32 [rows, width] tensor")
+    if gate.shape != x.shape or delta.shape != x.shape or not delta.is_contiguous():
+        raise KernelError(f"gated_residual_add: gate {tuple(gate.shape)} and delta {tuple(delta.shape)} must match x {tuple(x.shape)}")
+    if bias.dtype != torch.float32 or bias.numel() != x.shape[1] or not bias.is_contiguous():
+        raise KernelError(f"gated_residual_add: bias must be contiguous float32 of {x.shape[1]} elements")
+    lib = elementwise()
+    _run(lib, lib.mb_gated_residual_add(_p(x), _p(gate), gate.stride(0), _code(gate.dtype), _p(bias), _p(delta), _code(delta.dtype),
+                                        x.shape[0], x.shape[1], _stream()))
+    return x
+
+
 # ------------------------------------------------------------------------------------ attention
 
 def paged_attention_rows(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
@@ -474,6 +505,158 @@ def talking_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, 
         block_table.shape[1], _p(cu_q), _p(kv_lens), kv_lens.numel(), max_q_len, _p(talk), _p(gate),
         gate.stride(0) if gate is not None else 0, heads, kv_heads, head_dim, value_dim, page_size, window or 0, keep_first,
         ctypes.c_float(scale), ctypes.c_float(out_scale), _stream()))
+
+
+def gated_attention_library():
+    return load_library("mb_gated_attention", ["gated_attention.cu"])
+
+
+def norm_store(q: Optional[torch.Tensor], k: torch.Tensor, v: Optional[torch.Tensor], positions: torch.Tensor,
+               q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], eps: float, temperature_coef: float,
+               temperature_every: int, k_pool: torch.Tensor, v_pool: Optional[torch.Tensor], slot_mapping: torch.Tensor,
+               heads: int, kv_heads: int, head_dim: int, value_dim: int) -> None:
+    """Per head: q (in place) = q / rms(q) * q_gain * (1 + coef * ln(floor((p + 1) / every) + 1)); keys
+    k / rms(k) * k_gain and values (as they are) go into the pools at `slot_mapping`.  rms(x) = sqrt(mean(x^2) + eps)
+    over the head; a gain of None leaves that side as it is; `heads` 0: there are no queries (q None); `value_dim` 0:
+    there are no values (v, v_pool None).  q, k, v may be column slices of one tensor."""
+    _cuda(q, k, v, positions, q_gain, k_gain, k_pool, v_pool, slot_mapping)
+    _int32(positions, "positions")
+    _int32(slot_mapping, "slot_mapping")
+    tokens = k.shape[0]
+    for name, t, width in (("q", q, heads * head_dim), ("k", k, kv_heads * head_dim), ("v", v, kv_heads * value_dim)):
+        if t is None:
+            if width:
+                raise KernelError(f"norm_store: {name} is missing")
+            continue
+        _columns(t, name)
+        if t.shape[1] != width or t.shape[0] != tokens or t.dtype != k.dtype:
+            raise KernelError(f"norm_store: {name} is {tuple(t.shape)} {t.dtype}; [{tokens}, {width}] {k.dtype} is needed")
+    for name, gain in (("q_gain", q_gain), ("k_gain", k_gain)):
+        if gain is not None and (gain.dtype != torch.float32 or gain.numel() != head_dim or not gain.is_contiguous()):
+            raise KernelError(f"norm_store: {name} must be contiguous float32 of {head_dim} elements")
+    page_size = k_pool.shape[2]
+    if tuple(k_pool.shape[1:]) != (kv_heads, page_size, head_dim) or not k_pool.is_contiguous() or k_pool.dtype != k.dtype:
+        raise KernelError(f"norm_store: the key pool must be contiguous [pages, {kv_heads}, page_size, {head_dim}] of {k.dtype}")
+    if value_dim and (tuple(v_pool.shape[1:]) != (kv_heads, page_size, value_dim) or not v_pool.is_contiguous()
+                      or v_pool.dtype != k.dtype):
+        raise KernelError(f"norm_store: the value pool must be contiguous [pages, {kv_heads}, page_size, {value_dim}] of {k.dtype}")
+    lib = gated_attention_library()
+    _run(lib, lib.mb_norm_store(_p(q), q.stride(0) if q is not None else 0, _p(k), k.stride(0), _p(v),
+                                v.stride(0) if v is not None else 0, _code(k.dtype), _p(positions), _p(q_gain), _p(k_gain),
+                                ctypes.c_float(eps), ctypes.c_float(temperature_coef), int(temperature_every), _p(k_pool),
+                                _p(v_pool) if value_dim else None, _p(slot_mapping), tokens, heads, kv_heads, head_dim, value_dim,
+                                page_size, _stream()))
+
+
+GATE_KINDS = {None: 0, "head": 1, "element": 2}
+
+
+def gated_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: Optional[torch.Tensor],
+                    block_table: torch.Tensor, cu_q: torch.Tensor, kv_lens: torch.Tensor, max_q_len: int, heads: int,
+                    kv_heads: int, head_dim: int, value_dim: int, weights: str, scale: float, slope_exponent: float = 0.0,
+                    head_bias: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                    gate_kind: Optional[str] = None) -> None:
+    """Causal attention over the paged cache with `weights` "softmax" or "sigmoid" (independent sigmoids of the scores,
+    not normalised over keys); score = scale * q.k - 2^(-slope_exponent (h + 1) / heads) * (i - j) + head_bias[h]
+    (slope_exponent 0: no distance term; head_bias None: 0).  `v_pool` None: the values are the first `value_dim`
+    coordinates of the key rows.  gate_kind "head": out_h *= sigmoid(gate[:, h]); "element": out *= sigmoid(gate),
+    gate [T, heads * value_dim].  q [T, heads * head_dim], out [T, heads * value_dim] and gate may be column slices."""
+    if weights not in ("softmax", "sigmoid"):
+        raise KernelError(f"gated_attention: weights must be 'softmax' or 'sigmoid', got {weights!r}")
+    if gate_kind not in GATE_KINDS or (gate_kind is None) != (gate is None):
+        raise KernelError(f"gated_attention: gate kind {gate_kind!r} does not fit the gate given")
+    _cuda(q, out, k_pool, v_pool, block_table, cu_q, kv_lens, head_bias, gate)
+    _int32(block_table, "block_table")
+    _int32(cu_q, "cu_q")
+    _int32(kv_lens, "kv_lens")
+    _columns(q, "q")
+    _columns(out, "out")
+    if q.shape[1] != heads * head_dim or out.shape[1] != heads * value_dim or q.shape[0] != out.shape[0]:
+        raise KernelError(f"gated_attention: q {tuple(q.shape)} and out {tuple(out.shape)} do not fit {heads} heads of "
+                          f"{head_dim} and {value_dim}")
+    page_size = k_pool.shape[2]
+    if tuple(k_pool.shape[1:]) != (kv_heads, page_size, head_dim) or not k_pool.is_contiguous():
+        raise KernelError(f"gated_attention: the key pool must be contiguous [pages, {kv_heads}, page_size, {head_dim}]")
+    values = k_pool if v_pool is None else v_pool
+    if v_pool is not None and (tuple(v_pool.shape[1:]) != (kv_heads, page_size, value_dim) or not v_pool.is_contiguous()):
+        raise KernelError(f"gated_attention: the value pool must be contiguous [pages, {kv_heads}, page_size, {value_dim}]")
+    if v_pool is None and value_dim > head_dim:
+        raise KernelError(f"gated_attention: values of {value_dim} cannot be read from key rows of {head_dim}")
+    if not (q.dtype == out.dtype == k_pool.dtype == values.dtype):
+        raise KernelError("gated_attention: q, out and the pools must share one dtype")
+    if head_bias is not None and (head_bias.dtype != torch.float32 or head_bias.numel() != heads or not head_bias.is_contiguous()):
+        raise KernelError(f"gated_attention: head_bias must be contiguous float32 of {heads} elements")
+    if gate is not None:
+        _columns(gate, "gate")
+        if gate.dtype != q.dtype or tuple(gate.shape) != (q.shape[0], heads if gate_kind == "head" else heads * value_dim):
+            raise KernelError(f"gated_attention: a gate of kind {gate_kind!r} cannot be {tuple(gate.shape)} {gate.dtype}")
+    lib = gated_attention_library()
+    _run(lib, lib.mb_gated_attention_rows(
+        _p(q), q.stride(0), _p(out), out.stride(0), _code(q.dtype), _p(k_pool), _p(values), values.shape[3], _p(block_table),
+        block_table.shape[1], _p(cu_q), _p(kv_lens), _p(head_bias), _p(gate), gate.stride(0) if gate is not None else 0,
+        GATE_KINDS[gate_kind], kv_lens.numel(), max_q_len, heads, kv_heads, head_dim, value_dim, page_size,
+        1 if weights == "softmax" else 0, ctypes.c_float(scale), ctypes.c_float(slope_exponent), _stream()))
+
+
+def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, heads: int, gate: Optional[torch.Tensor] = None) -> None:
+    """One small matrix per head: out[t, h, :] = weight[h] . x[t, h, :] for weight [heads, n_out, n_in], x [T, heads * n_in],
+    out [T, heads * n_out] (column slices allowed); with `gate` [T, heads], out[t, h, :] *= sigmoid(gate[t, h])."""
+    _cuda(x, weight, out, gate)
+    _columns(x, "x")
+    _columns(out, "out")
+    if weight.dim() != 3 or weight.shape[0] != heads or not weight.is_contiguous():
+        raise KernelError(f"head_linear: weight must be contiguous [{heads}, n_out, n_in], got {tuple(weight.shape)}")
+    n_out, n_in = weight.shape[1], weight.shape[2]
+    if tuple(x.shape) != (out.shape[0], heads * n_in) or out.shape[1] != heads * n_out or not (x.dtype == weight.dtype == out.dtype):
+        raise KernelError(f"head_linear: x {tuple(x.shape)} {x.dtype} and out {tuple(out.shape)} {out.dtype} do not fit "
+                          f"{heads} matrices of {n_out} x {n_in} {weight.dtype}")
+    if gate is not None:
+        _columns(gate, "gate")
+        if tuple(gate.shape) != (x.shape[0], heads) or gate.dtype != x.dtype:
+            raise KernelError(f"head_linear: gate must be [{x.shape[0]}, {heads}] of x's dtype")
+    lib = gated_attention_library()
+    _run(lib, lib.mb_head_linear(_p(x), x.stride(0), _p(weight), _p(out), out.stride(0), _code(x.dtype), _p(gate),
+                                 gate.stride(0) if gate is not None else 0, x.shape[0], heads, n_in, n_out, _stream()))
+
+
+def retention_library():
+    return load_library("mb_retention", ["retention.cu"])
+
+
+def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, positions: torch.Tensor,
+                   cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int, decay: torch.Tensor,
+                   key_scale: float, eps: float, state: torch.Tensor, slots: torch.Tensor, cu_q: torch.Tensor, heads: int,
+                   head_dim: int, value_dim: int, out: torch.Tensor, out_scale: float = 1.0) -> None:
+    """Retention over the new tokens of every sequence: q and k rotated over their first `rotary_dim` coordinates
+    (split-half pairs, float32 tables by position), k times key_scale; S = decay_h S + k v^T from the sequence's row of
+    `state` (float32 [slots, heads, head_dim, value_dim], updated in place); o = S^T q; out = out_scale * o / rms(o) *
+    silu(g) per head, rms(o) = sqrt(mean(o^2) + eps).  q, k, v, g are column slices with one row stride."""
+    _cuda(q, k, v, g, positions, cos, sin, decay, state, slots, cu_q, out)
+    _int32(positions, "positions")
+    _int32(slots, "slots")
+    _int32(cu_q, "cu_q")
+    tokens = q.shape[0]
+    for name, t, width in (("q", q, heads * head_dim), ("k", k, heads * head_dim), ("v", v, heads * value_dim),
+                           ("g", g, heads * value_dim), ("out", out, heads * value_dim)):
+        _columns(t, name)
+        if tuple(t.shape) != (tokens, width) or t.dtype != q.dtype:
+            raise KernelError(f"retention_scan: {name} is {tuple(t.shape)} {t.dtype}; [{tokens}, {width}] {q.dtype} is needed")
+    if not (q.stride(0) == k.stride(0) == v.stride(0) == g.stride(0)):
+        raise KernelError("retention_scan: q, k, v and g must share one row stride")
+    if state.dtype != torch.float32 or tuple(state.shape[1:]) != (heads, head_dim, value_dim) or not state.is_contiguous():
+        raise KernelError(f"retention_scan: the state must be contiguous float32 [slots, {heads}, {head_dim}, {value_dim}]")
+    if decay.dtype != torch.float32 or decay.numel() != heads or not decay.is_contiguous():
+        raise KernelError(f"retention_scan: decay must be contiguous float32 of {heads} elements")
+    if rotary_dim:
+        if cos is None or sin is None or cos.dtype != torch.float32 or sin.dtype != torch.float32:
+            raise KernelError("retention_scan: rotation needs float32 cos/sin tables")
+        if cos.shape[-1] != rotary_dim // 2 or cos.shape != sin.shape or not cos.is_contiguous() or not sin.is_contiguous():
+            raise KernelError(f"retention_scan: cos/sin tables must be contiguous [positions, {rotary_dim // 2}]")
+    lib = retention_library()
+    _run(lib, lib.mb_retention_scan(_p(q), _p(k), _p(v), _p(g), q.stride(0), _code(q.dtype), _p(positions), _p(cos), _p(sin),
+                                    rotary_dim, _p(decay), ctypes.c_float(key_scale), ctypes.c_float(eps), _p(state), _p(slots),
+                                    _p(cu_q), cu_q.numel() - 1, heads, head_dim, value_dim, _p(out), out.stride(0),
+                                    ctypes.c_float(out_scale), _stream()))
 
 
 def gated_recurrence_library():

@@ -1,0 +1,148 @@
+"""A plain, slow statement of the Lovurax decoder: whole sequences, no cache, float64 on the CPU, one
+function per mechanism, written from the design's equations and sharing nothing with the package.
+
+A layer is pre-norm with gated residuals: with h = rmsnorm(x),
+    x <- x + sigmoid(Rg h + rb) * sublayer(h)
+first for the mixer, then (if the layer has one) for the feed-forward.  Mixers: `retention` (a linear
+recurrence with a fixed decay per head), `attention` (grouped heads, sigmoid weights, no softmax) and
+`latent_attention` (keys and values expanded from one low-rank row per position, softmax).  Weights are a
+dict name -> tensor; a configuration is the dict of the model's config.json.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+F = torch.float64
+
+
+def rms_norm(x, weight=None, eps=1e-6):
+    """x / sqrt(mean(x^2) + eps) over the last axis, times `weight` when there is one."""
+    y = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
+    return y if weight is None else y * weight
+
+
+def sigmoid(z):
+    return 1.0 / (1.0 + torch.exp(-z))
+
+
+def softplus(z):
+    return torch.log1p(torch.exp(-z.abs())) + torch.clamp(z, min=0.0)
+
+
+def xielu(z, p, q):
+    """z > 0: softplus(p) z^2 + z/2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2."""
+    ap, aq = softplus(p), 0.5 + softplus(q)
+    return torch.where(z > 0, ap * z * z + 0.5 * z, aq * (torch.expm1(torch.clamp(z, max=0.0)) - z) + 0.5 * z)
+
+
+def rotate_half(x, positions, dims, base):
+    """x [T, heads, dim]: coordinate i of the first `dims` is paired with i + dims/2; the pair (u, v) at
+    position p becomes (u cos a - v sin a, v cos a + u sin a), a = p * base^(-2i/dims).  The rest passes."""
+    if dims == 0:
+        return x
+    half = dims // 2
+    i = torch.arange(half, dtype=F)
+    angle = positions.to(F)[:, None] * base ** (-2.0 * i / dims)[None, :]
+    c, s = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+    u, v = x[..., :half], x[..., half:dims]
+    return torch.cat([u * c - v * s, v * c + u * s, x[..., dims:]], dim=-1)
+
+
+def retention(h, w, m, eps):
+    """S_t = decay S_(t-1) + k_t v_t^T, o_t = S_t^T q_t per head, from S = 0 at the start of the sequence;
+    o divided by its root mean square per head, times silu(G h), then the output matrix."""
+    T = h.shape[0]
+    H, D, Dv = m["heads"], m["dim"], m["vdim"]
+    pos = torch.arange(T)
+    rot = m.get("rot") or {"dims": 0, "base": 1.0}
+    q = rotate_half((h @ w["q"].T).view(T, H, D), pos, rot["dims"], rot["base"])
+    k = rotate_half((h @ w["k"].T).view(T, H, D), pos, rot["dims"], rot["base"]) * D ** -0.5
+    v = (h @ w["v"].T).view(T, H, Dv)
+    out = torch.zeros(T, H, Dv, dtype=F)
+    for head in range(H):
+        S = torch.zeros(D, Dv, dtype=F)
+        for t in range(T):
+            S = m["decay"][head] * S + torch.outer(k[t, head], v[t, head])
+            out[t, head] = S.T @ q[t, head]
+    out = rms_norm(out, None, eps).reshape(T, H * Dv)
+    g = h @ w["g"].T
+    return (out * (g * sigmoid(g))) @ w["o"].T
+
+
+def sigmoid_attention(h, w, m, eps):
+    """Grouped heads; queries and keys RMS-normed per head with a gain shared by the heads; the query at
+    position p times 1 + coef ln(floor((p + 1) / every) + 1); weight of key j <= i:
+    sigmoid(scale q.k - slope_h (i - j) + pb_h), slope_h = 2^(-8 (h + 1) / H); no normalisation over keys;
+    the heads side by side times sigmoid(G h), then the output matrix."""
+    T = h.shape[0]
+    H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    q = rms_norm((h @ w["q"].T).view(T, H, D), w["q.norm"], eps)
+    k = rms_norm((h @ w["k"].T).view(T, G, D), w["k.norm"], eps)
+    v = (h @ w["v"].T).view(T, G, Dv)
+    pos = torch.arange(T)
+    temp = m.get("q_temp")
+    if temp:
+        q = q * (1.0 + temp["coef"] * torch.log(torch.floor((pos + 1).to(F) / temp["every"]) + 1.0))[:, None, None]
+    out = torch.zeros(T, H, Dv, dtype=F)
+    distance = (pos[:, None] - pos[None, :]).to(F)
+    visible = distance >= 0
+    for head in range(H):
+        c = head // (H // G)
+        slope = 2.0 ** (-8.0 * (head + 1) / H)
+        score = (q[:, head] @ k[:, c].T) * m["scale"] - slope * distance
+        weight = torch.where(visible, sigmoid(score + w["pb"][head]), torch.zeros((), dtype=F))
+        out[:, head] = weight @ v[:, c]
+    return (out.reshape(T, H * Dv) * sigmoid(h @ w["g"].T)) @ w["o"].T
+
+
+def latent_attention(h, w, m, eps):
+    """c = rmsnorm(Dkv h) (the only thing a cache would keep); per head k = Uk c, v = Uv c; softmax over
+    j <= i of scale q.k; head h's result times sigmoid((G h)_h); then the output matrix."""
+    T = h.shape[0]
+    H, D, Dv = m["heads"], m["dim"], m["vdim"]
+    q = (h @ w["q"].T).view(T, H, D)
+    c = rms_norm(h @ w["dkv"].T, w["dkv.norm"], eps)
+    k = (c @ w["uk"].T).view(T, H, D)
+    v = (c @ w["uv"].T).view(T, H, Dv)
+    pos = torch.arange(T)
+    visible = pos[:, None] >= pos[None, :]
+    gate = sigmoid(h @ w["g"].T)
+    out = torch.zeros(T, H, Dv, dtype=F)
+    for head in range(H):
+        score = (q[:, head] @ k[:, head].T) * m["scale"]
+        score = torch.where(visible, score, torch.full((), -math.inf, dtype=F))
+        out[:, head] = torch.softmax(score, dim=-1) @ v[:, head] * gate[:, head:head + 1]
+    return out.reshape(T, H * Dv) @ w["o"].T
+
+
+def dense_feed_forward(h, w):
+    return xielu(h @ w["up"].T, w["act"][0], w["act"][1]) @ w["down"].T
+
+
+MIXERS = {"retention": retention, "attention": sigmoid_attention, "latent_attention": latent_attention}
+
+
+def sub(weights, prefix):
+    """The tensors under `prefix`, as float64, with the prefix taken off their names."""
+    return {name[len(prefix):]: t.to(F) for name, t in weights.items() if name.startswith(prefix)}
+
+
+def forward(config, weights, tokens, layers_out=None):
+    """Logits [T, vocab] of one whole sequence; `layers_out` (a list) receives the stream after every layer."""
+    eps = config["norm"]["eps"]
+    W = {n: t.to(F) for n, t in weights.items()}
+    x = W["embed"][torch.as_tensor(tokens, dtype=torch.long)]
+    for i, layer in enumerate(config["layers"]):
+        p = f"l{i}."
+        h = rms_norm(x, W[p + "norm1"], eps)
+        mixed = MIXERS[layer["type"]](h, sub(weights, p + "mix."), layer["mixer"], eps)
+        x = x + sigmoid(h @ W[p + "rg1"].T + W[p + "rg1.b"]) * mixed
+        if layer.get("mlp") is not None:
+            h = rms_norm(x, W[p + "norm2"], eps)
+            x = x + sigmoid(h @ W[p + "rg2"].T + W[p + "rg2.b"]) * dense_feed_forward(h, sub(weights, p + "mlp."))
+        if layers_out is not None:
+            layers_out.append(x.clone())
+    return rms_norm(x, W["final.norm"], eps) @ W["embed"].T * config.get("logit_scale", 1.0)
