@@ -66,7 +66,7 @@ class GatedResidualBlock(Part):
         proj = linear(h, w_in, dtype)
         w_out = part.output_matrix()
         mid = torch.empty((x.shape[0], w_out.shape[1]), dtype=dtype, device=x.device)
-        part.inner(proj[:, :gate_at], mid, batch, run, 1.0)
+        part.inner(proj[:, :part.input_matrix().shape[0]], mid, batch, run, 1.0)  # (rows of padding lie before the gate's)
         delta = linear(mid, w_out, torch.float32)
         ops.gated_residual_add(x, proj[:, gate_at:gate_at + self.width], bias, delta)
 

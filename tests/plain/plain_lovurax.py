@@ -15,6 +15,8 @@ import math
 
 import torch
 
+from .plain_llama import read_model_folder  # noqa: F401  (reads config.json and the safetensors file)
+
 F = torch.float64
 
 
@@ -38,22 +40,44 @@ def xielu(z, p, q):
     return torch.where(z > 0, ap * z * z + 0.5 * z, aq * (torch.expm1(torch.clamp(z, max=0.0)) - z) + 0.5 * z)
 
 
-def rotate_half(x, positions, dims, base):
+def rotate_half(x, positions, dims, base, angle_dtype=F):
     """x [T, heads, dim]: coordinate i of the first `dims` is paired with i + dims/2; the pair (u, v) at
-    position p becomes (u cos a - v sin a, v cos a + u sin a), a = p * base^(-2i/dims).  The rest passes."""
+    position p becomes (u cos a - v sin a, v cos a + u sin a), a = p * base^(-2i/dims).  The rest passes.
+    `angle_dtype` float32: the frequency and the angle are rounded to 32 bits, as the design computes them (far from
+    zero the angle's last bits are worth more than a float32 comparison forgives)."""
     if dims == 0:
         return x
     half = dims // 2
     i = torch.arange(half, dtype=F)
-    angle = positions.to(F)[:, None] * base ** (-2.0 * i / dims)[None, :]
+    angle = (positions.to(angle_dtype)[:, None] * (base ** (-2.0 * i / dims)).to(angle_dtype)[None, :]).to(F)
     c, s = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
     u, v = x[..., :half], x[..., half:dims]
     return torch.cat([u * c - v * s, v * c + u * s, x[..., dims:]], dim=-1)
 
 
+def retention_states(q, k, v, decay, start=None):
+    """The recurrence itself, token by token, for one head: S_t = decay S_(t-1) + k_t v_t^T from `start` (zeros by
+    default), o_t = S_t^T q_t.  q, k [T, D], v [T, Dv].  Returns o [T, Dv] and the last state."""
+    S = torch.zeros(q.shape[1], v.shape[1], dtype=F) if start is None else start.clone()
+    out = torch.zeros(q.shape[0], v.shape[1], dtype=F)
+    for t in range(q.shape[0]):
+        S = decay * S + torch.outer(k[t], v[t])
+        out[t] = S.T @ q[t]
+    return out, S
+
+
+def retention_sums(q, k, v, decay):
+    """The same o_t from a zero state, written out as sums: o_t = sum over j <= t of decay^(t - j) (q_t . k_j) v_j."""
+    T = q.shape[0]
+    t = torch.arange(T)
+    distance = (t[:, None] - t[None, :]).clamp(min=0).to(F)
+    weight = torch.where(t[:, None] >= t[None, :], torch.full((), float(decay), dtype=F) ** distance, torch.zeros((), dtype=F))
+    return ((q @ k.T) * weight) @ v
+
+
 def retention(h, w, m, eps):
-    """S_t = decay S_(t-1) + k_t v_t^T, o_t = S_t^T q_t per head, from S = 0 at the start of the sequence;
-    o divided by its root mean square per head, times silu(G h), then the output matrix."""
+    """Per head S_t = decay S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, from S = 0 at the start of the sequence, with q and k
+    rotated and k times dim^(-1/2); o divided by its root mean square per head, times silu(G h), then the output matrix."""
     T = h.shape[0]
     H, D, Dv = m["heads"], m["dim"], m["vdim"]
     pos = torch.arange(T)
@@ -61,12 +85,7 @@ def retention(h, w, m, eps):
     q = rotate_half((h @ w["q"].T).view(T, H, D), pos, rot["dims"], rot["base"])
     k = rotate_half((h @ w["k"].T).view(T, H, D), pos, rot["dims"], rot["base"]) * D ** -0.5
     v = (h @ w["v"].T).view(T, H, Dv)
-    out = torch.zeros(T, H, Dv, dtype=F)
-    for head in range(H):
-        S = torch.zeros(D, Dv, dtype=F)
-        for t in range(T):
-            S = m["decay"][head] * S + torch.outer(k[t, head], v[t, head])
-            out[t, head] = S.T @ q[t, head]
+    out = torch.stack([retention_sums(q[:, head], k[:, head], v[:, head], m["decay"][head]) for head in range(H)], dim=1)
     out = rms_norm(out, None, eps).reshape(T, H * Dv)
     g = h @ w["g"].T
     return (out * (g * sigmoid(g))) @ w["o"].T
