@@ -182,6 +182,188 @@ gated_attention_rows_kernel(const T* __restrict__ q, int q_stride, T* __restrict
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Decoding: one query token per sequence.  A warp per (sequence, head) cannot keep a GPU busy with a handful of
+// sequences, and it reads a key/value head once per query head that shares it.  Here the keys of a sequence are cut
+// into `splits` runs of `span` pages; a block owns one run of one key/value head and up to kGroup of the query heads
+// that share it, so a key or value row is read once for all of them.  Its four warps take the run's chunks of 32 keys
+// in turn (a lane a key for the scores, a lane a value coordinate for the sums), then meet in shared memory and write
+// one partial result per head: [maximum, sum of weights (softmax) or 1 (sigmoid), value_dim sums]; a run beyond the
+// sequence's end writes a sum of 0.  A second kernel adds the runs in their order (rescaled to the common maximum for
+// the softmax), applies the gate and stores the token's result: the same bits every time.
+
+// grid (splits, kv_heads * parts, sequences), parts = ceil((heads / kv_heads) / kGroup); block 128.
+// shared: q [kGroup][head_dim], then per warp [kGroup][2 + value_dim].
+template <typename T, int kGroup, int kAcc, bool kSoftmax>
+__global__ void __launch_bounds__(128)
+gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
+                              int v_width, const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
+                              const int* __restrict__ kv_lens, const float* __restrict__ head_bias, float* __restrict__ partial,
+                              int span, int heads, int kv_heads, int head_dim, int value_dim, int page_size, float scale,
+                              float slope_exponent) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    extern __shared__ __align__(16) float decode_shared[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seq = blockIdx.z, split = blockIdx.x, splits = gridDim.x;
+    const int group = heads / kv_heads, parts = (group + kGroup - 1) / kGroup;
+    const int kv_head = blockIdx.y / parts, part = blockIdx.y % parts;
+    const int head0 = kv_head * group + part * kGroup;
+    const int count = min(kGroup, group - part * kGroup);
+    const int pos = kv_lens[seq] - 1;
+    const int begin = split * span * page_size;
+    const int end = min(pos + 1, begin + span * page_size);
+    const int stride = 2 + value_dim;
+    float* q_shared = decode_shared;
+    float* meet = decode_shared + kGroup * head_dim;  // [warp][kGroup][stride]
+    if (begin >= end) {  // nothing of the sequence lies in this run (the whole block leaves)
+        for (int g = threadIdx.x; g < count; g += blockDim.x) {
+            float* dst = partial + (((size_t)seq * heads + head0 + g) * splits + split) * stride;
+            dst[0] = -CUDART_INF_F;
+            dst[1] = 0.0f;
+        }
+        return;
+    }
+    const T* q_row = q + (size_t)cu_q[seq] * q_stride + (size_t)head0 * head_dim;
+    for (int i = threadIdx.x; i < count * head_dim; i += blockDim.x) q_shared[i] = Num<T>::load(q_row + i);
+    __syncthreads();
+    const bool vector_ok = (head_dim % 8) == 0 && (((size_t)k_pool) & (sizeof(T) * 8 - 1)) == 0;
+    float slope[kGroup], bias[kGroup], run_max[kGroup], run_sum[kGroup], acc[kGroup][kAcc];
+#pragma unroll
+    for (int g = 0; g < kGroup; ++g) {
+        slope[g] = slope_exponent != 0.0f ? exp2f(-slope_exponent * (float)(head0 + g + 1) / (float)heads) : 0.0f;
+        bias[g] = (head_bias != nullptr && g < count) ? head_bias[head0 + g] : 0.0f;
+        run_max[g] = -CUDART_INF_F;
+        run_sum[g] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kAcc; ++i) acc[g][i] = 0.0f;
+    }
+    const int* table = block_table + (size_t)seq * max_blocks;
+    for (int chunk = begin + warp * 32; chunk < end; chunk += 4 * 32) {
+        const size_t page = table[chunk / page_size];
+        const size_t base = (page * kv_heads + kv_head) * page_size + (chunk % page_size);
+        const int p = chunk + lane;
+        const bool visible = p < end;
+        float score[kGroup];
+#pragma unroll
+        for (int g = 0; g < kGroup; ++g) score[g] = 0.0f;
+        if (visible) {
+            const T* k_row = k_pool + (base + lane) * head_dim;
+            if (vector_ok) {
+                for (int d = 0; d < head_dim; d += 8) {
+                    float kv[8];
+                    load8(k_row + d, kv);
+#pragma unroll
+                    for (int g = 0; g < kGroup; ++g)
+                        if (g < count) {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) score[g] = fmaf(q_shared[g * head_dim + d + i], kv[i], score[g]);
+                        }
+                }
+            } else {
+                for (int d = 0; d < head_dim; ++d) {
+                    const float kd = Num<T>::load(k_row + d);
+#pragma unroll
+                    for (int g = 0; g < kGroup; ++g)
+                        if (g < count) score[g] = fmaf(q_shared[g * head_dim + d], kd, score[g]);
+                }
+            }
+        }
+        float weight[kGroup];
+#pragma unroll
+        for (int g = 0; g < kGroup; ++g) {
+            const float z = visible ? score[g] * scale - slope[g] * (float)(pos - p) + bias[g] : -CUDART_INF_F;
+            if (kSoftmax) {
+                const float new_max = fmaxf(run_max[g], warp_max(z));  // finite: the chunk holds a visible key
+                weight[g] = visible ? expf(z - new_max) : 0.0f;
+                const float correction = expf(run_max[g] - new_max);
+                run_sum[g] = run_sum[g] * correction + warp_sum(weight[g]);
+                run_max[g] = new_max;
+#pragma unroll
+                for (int i = 0; i < kAcc; ++i) acc[g][i] *= correction;
+            } else {
+                weight[g] = visible ? sigmoid(z) : 0.0f;
+            }
+        }
+        const int last = min(31, end - 1 - chunk);
+        for (int jj = 0; jj <= last; ++jj) {
+            const T* v_row = v_pool + (base + jj) * v_width;
+            float value[kAcc];
+#pragma unroll
+            for (int i = 0; i < kAcc; ++i) value[i] = lane + 32 * i < value_dim ? Num<T>::load(v_row + lane + 32 * i) : 0.0f;
+#pragma unroll
+            for (int g = 0; g < kGroup; ++g) {
+                const float w = __shfl_sync(0xffffffffu, weight[g], jj);
+#pragma unroll
+                for (int i = 0; i < kAcc; ++i) acc[g][i] = fmaf(w, value[i], acc[g][i]);
+            }
+        }
+    }
+    // the warps meet: every warp leaves its maxima, sums and value sums; the first `count` threads' warps add them in warp order
+#pragma unroll
+    for (int g = 0; g < kGroup; ++g) {
+        if (g < count) {
+            float* mine = meet + ((size_t)warp * kGroup + g) * stride;
+            if (lane == 0) {
+                mine[0] = run_max[g];
+                mine[1] = run_sum[g];
+            }
+#pragma unroll
+            for (int i = 0; i < kAcc; ++i)
+                if (lane + 32 * i < value_dim) mine[2 + lane + 32 * i] = acc[g][i];
+        }
+    }
+    __syncthreads();
+    for (int item = threadIdx.x; item < count * value_dim; item += blockDim.x) {
+        const int g = item / value_dim, d = item % value_dim;
+        float top = -CUDART_INF_F;
+        if (kSoftmax)
+            for (int w = 0; w < 4; ++w) top = fmaxf(top, meet[((size_t)w * kGroup + g) * stride]);
+        float sum = 0.0f, weights = 0.0f;
+        for (int w = 0; w < 4; ++w) {
+            const float* theirs = meet + ((size_t)w * kGroup + g) * stride;
+            const float factor = kSoftmax ? (theirs[0] == -CUDART_INF_F ? 0.0f : expf(theirs[0] - top)) : 1.0f;
+            sum = fmaf(theirs[2 + d], factor, sum);
+            weights = fmaf(theirs[1], factor, weights);
+        }
+        float* dst = partial + (((size_t)seq * heads + head0 + g) * splits + split) * stride;
+        dst[2 + d] = sum;
+        if (d == 0) {
+            dst[0] = top;
+            dst[1] = kSoftmax ? weights : 1.0f;
+        }
+    }
+}
+
+// grid (heads, sequences); block: value_dim rounded up to a multiple of 32.
+template <typename T, bool kSoftmax>
+__global__ void gated_attention_combine_kernel(const float* __restrict__ partial, int splits, T* __restrict__ out, int out_stride,
+                                               const int* __restrict__ cu_q, const T* __restrict__ gate, int gate_stride,
+                                               int gate_kind, int heads, int value_dim) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int head = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
+    if (d >= value_dim) return;
+    const int stride = 2 + value_dim;
+    const float* mine = partial + ((size_t)seq * heads + head) * splits * stride;
+    float top = -CUDART_INF_F;
+    if (kSoftmax)
+        for (int s = 0; s < splits; ++s) top = fmaxf(top, mine[(size_t)s * stride]);
+    float sum = 0.0f, weights = 0.0f;
+    for (int s = 0; s < splits; ++s) {
+        const float* run = mine + (size_t)s * stride;
+        if (run[1] == 0.0f) continue;  // a run beyond the sequence's end
+        const float factor = kSoftmax ? expf(run[0] - top) : 1.0f;
+        sum = fmaf(run[2 + d], factor, sum);
+        weights = fmaf(run[1], factor, weights);
+    }
+    float value = kSoftmax ? sum / weights : sum;
+    const size_t row = cu_q[seq];
+    if (gate_kind == kGateHead) value *= sigmoid(Num<T>::load(gate + row * gate_stride + head));
+    if (gate_kind == kGateElement) value *= sigmoid(Num<T>::load(gate + row * gate_stride + (size_t)head * value_dim + d));
+    Num<T>::store(out + row * out_stride + (size_t)head * value_dim + d, value);
+}
+
 // out[t, h * n_out + n] = gate * sum_k in[t, h * n_in + k] * w[(h * n_out + n) * n_in + k]: one small matrix per head,
 // rows of n_in weights; gate: sigmoid of gate[t, h] when given.  grid (ceil(tokens / kRows), heads); block 128.
 // shared: kRows * n_in floats.
@@ -307,6 +489,77 @@ MB_EXPORT int mb_gated_attention_rows(const void* q, int q_stride, void* out, in
         return fail("gated_attention_rows: unknown dtype code %d", dtype);
 #undef MB_ROWS
     return status ? status : check_launch("gated_attention_rows");
+}
+
+namespace mb {
+
+template <typename T, int kGroup, int kAcc, bool kSoftmax>
+int launch_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pool, const void* v_pool, int v_width,
+                  const int* block_table, int max_blocks, const int* cu_q, const int* kv_lens, const float* head_bias,
+                  const void* gate, int gate_stride, int gate_kind, int sequences, int heads, int kv_heads, int head_dim,
+                  int value_dim, int page_size, float scale, float slope_exponent, int splits, int span, float* partial,
+                  cudaStream_t stream) {
+    const int group = heads / kv_heads, parts = (group + kGroup - 1) / kGroup;
+    const size_t smem = ((size_t)kGroup * head_dim + 4 * (size_t)kGroup * (2 + value_dim)) * sizeof(float);
+    auto kernel = gated_attention_decode_kernel<T, kGroup, kAcc, kSoftmax>;
+    if (smem > 48 * 1024) {
+        cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (status != cudaSuccess) return fail("gated_attention_decode: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(status));
+    }
+    MB_LAUNCH("gated_attention_decode", kernel, dim3(splits, kv_heads * parts, sequences), dim3(128), smem, stream, true, (const T*)q,
+              q_stride, (const T*)k_pool, (const T*)v_pool, v_width, block_table, max_blocks, cu_q, kv_lens, head_bias, partial, span,
+              heads, kv_heads, head_dim, value_dim, page_size, scale, slope_exponent);
+    MB_LAUNCH("gated_attention_combine", (gated_attention_combine_kernel<T, kSoftmax>), dim3(heads, sequences),
+              dim3((value_dim + 31) / 32 * 32), 0, stream, true, (const float*)partial, splits, (T*)out, out_stride, cu_q,
+              (const T*)gate, gate_stride, gate_kind, heads, value_dim);
+    return 0;
+}
+
+template <typename T, bool kSoftmax, typename... Args>
+int pick_decode(int group, int value_dim, Args... args) {
+    if (value_dim <= 128) return group <= 4 ? launch_decode<T, 4, 4, kSoftmax>(args...) : launch_decode<T, 8, 4, kSoftmax>(args...);
+    if (value_dim <= 256) return group <= 4 ? launch_decode<T, 4, 8, kSoftmax>(args...) : launch_decode<T, 8, 8, kSoftmax>(args...);
+    return launch_decode<T, 4, 16, kSoftmax>(args...);
+}
+
+}  // namespace mb
+
+// Floats of scratch a decode call with `splits` runs needs.
+MB_EXPORT size_t mb_gated_attention_decode_scratch_floats(int sequences, int heads, int value_dim, int splits) {
+    return (size_t)sequences * heads * splits * (2 + value_dim);
+}
+
+// One token per sequence (row cu_q[s] of q and out).  The keys are cut into `splits` runs of `span` pages
+// (splits * span * page_size must cover the longest sequence); `partial` holds mb_gated_attention_decode_scratch_floats floats.
+MB_EXPORT int mb_gated_attention_decode(const void* q, int q_stride, void* out, int out_stride, int dtype, const void* k_pool,
+                                        const void* v_pool, int v_width, const int* block_table, int max_blocks, const int* cu_q,
+                                        const int* kv_lens, const float* head_bias, const void* gate, int gate_stride, int gate_kind,
+                                        int sequences, int heads, int kv_heads, int head_dim, int value_dim, int page_size,
+                                        int softmax, float scale, float slope_exponent, int splits, int span, float* partial,
+                                        cudaStream_t stream) {
+    if (sequences <= 0) return 0;
+    if (head_dim <= 0 || head_dim > 2048) return fail("gated_attention_decode: head_dim %d is outside 1..2048", head_dim);
+    if (value_dim <= 0 || value_dim > 512 || value_dim > v_width)
+        return fail("gated_attention_decode: value_dim %d is outside 1..512 or beyond the value rows of %d", value_dim, v_width);
+    if (kv_heads <= 0 || heads % kv_heads) return fail("gated_attention_decode: %d heads are no multiple of %d kv heads", heads, kv_heads);
+    if (page_size <= 0 || page_size % 32) return fail("gated_attention_decode: page_size %d must be a multiple of 32", page_size);
+    if (splits < 1 || span < 1 || splits > 65535) return fail("gated_attention_decode: %d runs of %d pages", splits, span);
+    if (sequences > 65535 || heads > 65535) return fail("gated_attention_decode: %d sequences or %d heads exceed the grid limit 65535", sequences, heads);
+    if (gate_kind < 0 || gate_kind > 2 || (gate_kind != 0 && gate == nullptr)) return fail("gated_attention_decode: gate kind %d", gate_kind);
+    if (partial == nullptr) return fail("gated_attention_decode: no scratch memory");
+    int status;
+#define MB_DECODE(T, S)                                                                                                          \
+    mb::pick_decode<T, S>(heads / kv_heads, value_dim, q, q_stride, out, out_stride, k_pool, v_pool, v_width, block_table,       \
+                          max_blocks, cu_q, kv_lens, head_bias, gate, gate_stride, gate_kind, sequences, heads, kv_heads, head_dim, \
+                          value_dim, page_size, scale, slope_exponent, splits, span, partial, stream)
+    if (dtype == MB_F32)
+        status = softmax ? MB_DECODE(float, true) : MB_DECODE(float, false);
+    else if (dtype == MB_BF16)
+        status = softmax ? MB_DECODE(__nv_bfloat16, true) : MB_DECODE(__nv_bfloat16, false);
+    else
+        return fail("gated_attention_decode: unknown dtype code %d", dtype);
+#undef MB_DECODE
+    return status ? status : check_launch("gated_attention_decode");
 }
 
 MB_EXPORT int mb_head_linear(const void* in, int in_stride, const void* w, void* out, int out_stride, int dtype, const void* gate,

@@ -12,27 +12,41 @@
 // A block owns one (sequence, head): a thread per value coordinate j keeps column j of S in shared memory
 // ([head_dim][value_dim], so that neighbouring threads touch neighbouring words) and walks the sequence's new tokens
 // in order.  The state is read from the state area when the block starts and written back when it ends.
+//
+// The recurrence is linear in S, so a step of many tokens is cut into runs of `run_length` consecutive tokens that are
+// walked at the same time, in three kernels: every run first walks its tokens from a zero state and leaves what it
+// adds, B_r = sum_j decay^(n_r - 1 - j) k_j v_j^T, in scratch memory; then, element by element, the runs' starting
+// states follow from the stored state in run order, S_(r+1) = decay^(n_r) S_r + B_r (the last one is the sequence's new
+// state); then every run walks its tokens again from its starting state and writes the results.
 #include "common.cuh"
 
 MB_DEFINE_LAST_ERROR()
 
 namespace mb {
 
-// grid (heads, sequences); block: value_dim rounded up to a multiple of 32 (at most 1024).
+constexpr int kWhole = 0;      // one run: from the stored state, results written, the state stored
+constexpr int kSummarise = 1;  // a run from a zero state, no results: what it adds goes to scratch [run]
+constexpr int kEmit = 2;       // a run from its starting state in scratch [run], results written
+
+// grid (heads, sequences, runs); block: value_dim rounded up to a multiple of 32 (at most 1024).
 // shared: S [head_dim * value_dim], q [2][head_dim], k [2][head_dim], 32 floats for sums.
-template <typename T>
+// scratch: [sequence][head][run][head_dim * value_dim] floats.
+template <typename T, int kMode>
 __global__ void __launch_bounds__(1024)
 retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ g,
                       int in_stride, const int* __restrict__ positions, const float* __restrict__ cos_table,
                       const float* __restrict__ sin_table, int rotary_dim, const float* __restrict__ decay, float key_scale,
                       float eps, float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu_q,
-                      int heads, int head_dim, int value_dim, T* __restrict__ out, int out_stride, float out_scale) {
+                      int heads, int head_dim, int value_dim, T* __restrict__ out, int out_stride, float out_scale,
+                      int run_length, float* __restrict__ scratch) {
     grid_launch_dependents();
     grid_dependency_wait();
     extern __shared__ __align__(16) float shared[];
-    const int head = blockIdx.x, seq = blockIdx.y;
-    const int first = cu_q[seq];
-    const int count = cu_q[seq + 1] - first;
+    const int head = blockIdx.x, seq = blockIdx.y, run = blockIdx.z;
+    const int sequence_first = cu_q[seq];
+    const int sequence_count = cu_q[seq + 1] - sequence_first;
+    const int first = sequence_first + run * run_length;
+    const int count = kMode == kWhole ? sequence_count : min(run_length, sequence_count - run * run_length);
     if (count <= 0) return;  // the whole block leaves
     float* S = shared;
     float* qk = S + (size_t)head_dim * value_dim;  // [2 buffers][q | k][head_dim]
@@ -41,9 +55,10 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
     const bool live = j < value_dim;
     const int half = rotary_dim / 2;
     const float a = decay[head];
-    float* stored = state + ((size_t)slots[seq] * heads + head) * head_dim * value_dim;
+    float* stored = kMode == kWhole ? state + ((size_t)slots[seq] * heads + head) * head_dim * value_dim
+                                    : scratch + (((size_t)seq * heads + head) * gridDim.z + run) * head_dim * value_dim;
     if (live)
-        for (int d = 0; d < head_dim; ++d) S[d * value_dim + j] = stored[(size_t)d * value_dim + j];
+        for (int d = 0; d < head_dim; ++d) S[d * value_dim + j] = kMode == kSummarise ? 0.0f : stored[(size_t)d * value_dim + j];
 
     // rotated query and scaled rotated key of token t into buffer `b`
     auto stage = [&](int t, int b) {
@@ -84,6 +99,10 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
                 o = fmaf(s, qs[d], o);
             }
         }
+        if (kMode == kSummarise) {
+            __syncthreads();  // the other buffer is staged, and nobody still reads this one
+            continue;
+        }
         const float ssq = block_sum(o * o, sums);  // (two barriers inside: the other buffer is staged when it returns)
         if (live) {
             const float gate = Num<T>::load(g + (size_t)(first + t) * in_stride + (size_t)head * value_dim + j);
@@ -92,8 +111,34 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
         }
         __syncthreads();  // nobody still reads buffer b when the next round stages over it
     }
-    if (live)
+    if (live && kMode != kEmit)
         for (int d = 0; d < head_dim; ++d) stored[(size_t)d * value_dim + j] = S[d * value_dim + j];
+}
+
+// The runs' starting states, element by element in run order: scratch [run] holds what run `run` adds and receives the
+// state the run starts from; the state after the last run goes back to the state area.
+// grid (ceil(head_dim * value_dim / 256), heads, sequences); block 256.
+__global__ void retention_prefix_kernel(float* __restrict__ scratch, float* __restrict__ state, const int* __restrict__ slots,
+                                        const int* __restrict__ cu_q, const float* __restrict__ decay, int heads, int elements,
+                                        int runs, int run_length) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int head = blockIdx.y, seq = blockIdx.z;
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    const int count = cu_q[seq + 1] - cu_q[seq];
+    if (e >= elements || count <= 0) return;
+    float* stored = state + ((size_t)slots[seq] * heads + head) * elements + e;
+    float* mine = scratch + ((size_t)seq * heads + head) * runs * elements + e;
+    const float a = decay[head];
+    const float whole_run = powf(a, (float)run_length);
+    float s = *stored;
+    for (int run = 0; run * run_length < count; ++run) {
+        const int n = min(run_length, count - run * run_length);
+        const float added = mine[(size_t)run * elements];
+        mine[(size_t)run * elements] = s;
+        s = fmaf(n == run_length ? whole_run : powf(a, (float)n), s, added);
+    }
+    *stored = s;
 }
 
 }  // namespace mb
@@ -103,33 +148,72 @@ using namespace mb;
 // q, k: [tokens, >= heads * head_dim]; v, g: [tokens, >= heads * value_dim]; all four column slices of one tensor
 // (one row stride).  state: float [slots, heads, head_dim, value_dim]; slots[sequence] picks the row.
 // rotary_dim 0: no rotation (the tables may then be null).
+MB_EXPORT size_t mb_retention_scratch_floats(int sequences, int heads, int head_dim, int value_dim, int max_q_len, int run_length) {
+    if (run_length <= 0 || max_q_len <= run_length) return 0;
+    return (size_t)sequences * heads * ((max_q_len + run_length - 1) / run_length) * head_dim * value_dim;
+}
+
+namespace mb {
+
+template <typename T>
+int launch_retention(const void* q, const void* k, const void* v, const void* g, int in_stride, const int* positions,
+                     const float* cos_table, const float* sin_table, int rotary_dim, const float* decay, float key_scale, float eps,
+                     float* state, const int* slots, const int* cu_q, int sequences, int heads, int head_dim, int value_dim, void* out,
+                     int out_stride, float out_scale, int max_q_len, int run_length, float* scratch, size_t smem, cudaStream_t stream) {
+    const dim3 block((value_dim + 31) / 32 * 32);
+    const int runs = (run_length > 0 && max_q_len > run_length) ? (max_q_len + run_length - 1) / run_length : 1;
+    if (smem > 48 * 1024) {
+        cudaFuncSetAttribute(retention_scan_kernel<T, kWhole>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(retention_scan_kernel<T, kSummarise>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(retention_scan_kernel<T, kEmit>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
+#define MB_SCAN(MODE, RUNS)                                                                                                      \
+    MB_LAUNCH("retention_scan", (retention_scan_kernel<T, MODE>), dim3(heads, sequences, RUNS), dim3(block), smem, stream, true,  \
+              (const T*)q, (const T*)k, (const T*)v, (const T*)g, in_stride, positions, cos_table, sin_table, rotary_dim, decay,  \
+              key_scale, eps, state, slots, cu_q, heads, head_dim, value_dim, (T*)out, out_stride, out_scale, run_length, scratch)
+    if (runs == 1) {
+        MB_SCAN(kWhole, 1);
+        return 0;
+    }
+    const int elements = head_dim * value_dim;
+    MB_SCAN(kSummarise, runs);
+    MB_LAUNCH("retention_prefix", retention_prefix_kernel, dim3((elements + 255) / 256, heads, sequences), dim3(256), 0, stream, true,
+              scratch, state, slots, cu_q, decay, heads, elements, runs, run_length);
+    MB_SCAN(kEmit, runs);
+#undef MB_SCAN
+    return 0;
+}
+
+}  // namespace mb
+
+// q, k: [tokens, >= heads * head_dim]; v, g: [tokens, >= heads * value_dim]; all four column slices of one tensor
+// (one row stride).  state: float [slots, heads, head_dim, value_dim]; slots[sequence] picks the row.
+// rotary_dim 0: no rotation (the tables may then be null).  With max_q_len > run_length > 0 the sequences are walked in
+// runs of run_length tokens at once, and scratch must hold mb_retention_scratch_floats floats.
 MB_EXPORT int mb_retention_scan(const void* q, const void* k, const void* v, const void* g, int in_stride, int dtype,
                                 const int* positions, const float* cos_table, const float* sin_table, int rotary_dim,
                                 const float* decay, float key_scale, float eps, float* state, const int* slots, const int* cu_q,
                                 int sequences, int heads, int head_dim, int value_dim, void* out, int out_stride, float out_scale,
-                                cudaStream_t stream) {
+                                int max_q_len, int run_length, float* scratch, cudaStream_t stream) {
     if (sequences <= 0 || heads <= 0) return 0;
     if (head_dim <= 0 || value_dim <= 0 || value_dim > 1024) return fail("retention_scan: head_dim %d, value_dim %d (at most 1024)", head_dim, value_dim);
     if (rotary_dim < 0 || rotary_dim % 2 || rotary_dim > head_dim) return fail("retention_scan: rotary_dim %d must be even and at most %d", rotary_dim, head_dim);
     if (rotary_dim > 0 && (cos_table == nullptr || sin_table == nullptr)) return fail("retention_scan: rotation needs its tables");
     if (sequences > 65535) return fail("retention_scan: %d sequences exceed the grid limit 65535", sequences);
+    if (run_length > 0 && max_q_len > run_length && scratch == nullptr) return fail("retention_scan: runs need scratch memory");
+    if (run_length > 0 && (max_q_len + run_length - 1) / run_length > 65535) return fail("retention_scan: too many runs");
     const size_t smem = ((size_t)head_dim * value_dim + 4 * head_dim + 32) * sizeof(float);
     if (smem > 227 * 1024) return fail("retention_scan: a state of %d x %d floats exceeds a block's shared memory", head_dim, value_dim);
-    const dim3 grid(heads, sequences), block((value_dim + 31) / 32 * 32);
-    if (dtype == MB_F32) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(retention_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        MB_LAUNCH("retention_scan", retention_scan_kernel<float>, dim3(grid), dim3(block), smem, stream, true, (const float*)q,
-                  (const float*)k, (const float*)v, (const float*)g, in_stride, positions, cos_table, sin_table, rotary_dim, decay,
-                  key_scale, eps, state, slots, cu_q, heads, head_dim, value_dim, (float*)out, out_stride, out_scale);
-    } else if (dtype == MB_BF16) {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(retention_scan_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        MB_LAUNCH("retention_scan", retention_scan_kernel<__nv_bfloat16>, dim3(grid), dim3(block), smem, stream, true,
-                  (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const __nv_bfloat16*)g, in_stride,
-                  positions, cos_table, sin_table, rotary_dim, decay, key_scale, eps, state, slots, cu_q, heads, head_dim, value_dim,
-                  (__nv_bfloat16*)out, out_stride, out_scale);
-    } else {
+    int status;
+    if (dtype == MB_F32)
+        status = launch_retention<float>(q, k, v, g, in_stride, positions, cos_table, sin_table, rotary_dim, decay, key_scale, eps, state,
+                                         slots, cu_q, sequences, heads, head_dim, value_dim, out, out_stride, out_scale, max_q_len,
+                                         run_length, scratch, smem, stream);
+    else if (dtype == MB_BF16)
+        status = launch_retention<__nv_bfloat16>(q, k, v, g, in_stride, positions, cos_table, sin_table, rotary_dim, decay, key_scale, eps,
+                                                 state, slots, cu_q, sequences, heads, head_dim, value_dim, out, out_stride, out_scale,
+                                                 max_q_len, run_length, scratch, smem, stream);
+    else
         return fail("retention_scan: unknown dtype code %d", dtype);
-    }
-    return check_launch("retention_scan");
+    return status ? status : check_launch("retention_scan");
 }

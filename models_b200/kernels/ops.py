@@ -551,18 +551,55 @@ def norm_store(q: Optional[torch.Tensor], k: torch.Tensor, v: Optional[torch.Ten
 GATE_KINDS = {None: 0, "head": 1, "element": 2}
 
 
+def gated_attention_tc_library(key_dim: int, value_dim: int, shared_rows: bool):
+    """The tensor-core form, compiled for these key and value sizes at first use."""
+    return load_library("mb_gated_attention_tc", ["gated_attention_tc.cu"],
+                        {"MB_KEY_DIM": int(key_dim), "MB_VALUE_DIM": int(value_dim), "MB_SHARED_ROWS": 1 if shared_rows else 0})
+
+
+GATED_TC_MIN_ROWS = 8  # steps that bring fewer tokens to every sequence go to the kernel with a warp per (token, head)
+
+
+def gated_attention_tc_takes(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, head_dim: int, value_dim: int,
+                             max_q_len: int, gate: Optional[torch.Tensor], gate_kind: Optional[str] = "element") -> bool:
+    """bfloat16, cache pages of 64, key and value sizes multiples of 16 up to 256, 16-byte query rows."""
+    if q.dtype != torch.bfloat16 or max_q_len < GATED_TC_MIN_ROWS or k_pool.shape[2] != 64:
+        return False
+    if head_dim % 16 or value_dim % 16 or not 16 <= head_dim <= 256 or not 16 <= value_dim <= 256:
+        return False
+    if q.stride(0) % 8 or q.data_ptr() % 16 or out.stride(0) % 2 or out.data_ptr() % 4 or k_pool.data_ptr() % 16:
+        return False
+    return gate is None or gate_kind != "element" or (gate.stride(0) % 2 == 0 and gate.data_ptr() % 4 == 0)
+
+
+def gated_decode_runs(sequences: int, heads: int, kv_heads: int, pages: int, multiprocessors: int = 148):
+    """(runs, pages per run) for a decode step whose page tables are `pages` wide: as many runs as give every
+    multiprocessor two blocks, at most one per page and at most 64."""
+    group = heads // kv_heads
+    blocks = sequences * kv_heads * (-(-group // (4 if group <= 4 else 8)))
+    wanted = max(1, min(64, pages, -(-2 * multiprocessors // blocks)))
+    span = -(-pages // wanted)
+    return -(-pages // span), span
+
+
 def gated_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: Optional[torch.Tensor],
                     block_table: torch.Tensor, cu_q: torch.Tensor, kv_lens: torch.Tensor, max_q_len: int, heads: int,
                     kv_heads: int, head_dim: int, value_dim: int, weights: str, scale: float, slope_exponent: float = 0.0,
                     head_bias: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
-                    gate_kind: Optional[str] = None) -> None:
+                    gate_kind: Optional[str] = None, kernel: Optional[str] = None) -> None:
     """Causal attention over the paged cache with `weights` "softmax" or "sigmoid" (independent sigmoids of the scores,
     not normalised over keys); score = scale * q.k - 2^(-slope_exponent (h + 1) / heads) * (i - j) + head_bias[h]
     (slope_exponent 0: no distance term; head_bias None: 0).  `v_pool` None: the values are the first `value_dim`
     coordinates of the key rows.  gate_kind "head": out_h *= sigmoid(gate[:, h]); "element": out *= sigmoid(gate),
-    gate [T, heads * value_dim].  q [T, heads * head_dim], out [T, heads * value_dim] and gate may be column slices."""
+    gate [T, heads * value_dim].  q [T, heads * head_dim], out [T, heads * value_dim] and gate may be column slices.
+    `kernel`: None picks the decode form for steps of one token per sequence (the keys cut into runs with a block each;
+    the grid follows the page table's width, not the lengths, so that a captured step stays valid), the tensor-core form
+    where it applies (bfloat16 steps of many tokens), else the form with a warp per (token, head); "decode", "tc" or
+    "rows" asks for one of them."""
     if weights not in ("softmax", "sigmoid"):
         raise KernelError(f"gated_attention: weights must be 'softmax' or 'sigmoid', got {weights!r}")
+    if kernel not in (None, "tc", "rows", "decode"):
+        raise KernelError(f"gated_attention: unknown kernel {kernel!r}")
     if gate_kind not in GATE_KINDS or (gate_kind is None) != (gate is None):
         raise KernelError(f"gated_attention: gate kind {gate_kind!r} does not fit the gate given")
     _cuda(q, out, k_pool, v_pool, block_table, cu_q, kv_lens, head_bias, gate)
@@ -590,12 +627,39 @@ def gated_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_
         _columns(gate, "gate")
         if gate.dtype != q.dtype or tuple(gate.shape) != (q.shape[0], heads if gate_kind == "head" else heads * value_dim):
             raise KernelError(f"gated_attention: a gate of kind {gate_kind!r} cannot be {tuple(gate.shape)} {gate.dtype}")
+    softmax = 1 if weights == "softmax" else 0
+    sequences = kv_lens.numel()
+    gate_stride = gate.stride(0) if gate is not None else 0
+    if kernel == "decode" or (kernel is None and max_q_len == 1):
+        if max_q_len != 1:
+            raise KernelError("the decode form takes one token per sequence")
+        runs, span = gated_decode_runs(sequences, heads, kv_heads, block_table.shape[1], _sm_count(q.device))
+        lib = gated_attention_library()
+        lib.mb_gated_attention_decode_scratch_floats.restype = ctypes.c_size_t
+        scratch = torch.empty((lib.mb_gated_attention_decode_scratch_floats(sequences, heads, value_dim, runs),), dtype=torch.float32,
+                              device=q.device)
+        _run(lib, lib.mb_gated_attention_decode(
+            _p(q), q.stride(0), _p(out), out.stride(0), _code(q.dtype), _p(k_pool), _p(values), values.shape[3], _p(block_table),
+            block_table.shape[1], _p(cu_q), _p(kv_lens), _p(head_bias), _p(gate), gate_stride, GATE_KINDS[gate_kind], sequences,
+            heads, kv_heads, head_dim, value_dim, page_size, softmax, ctypes.c_float(scale), ctypes.c_float(slope_exponent), runs,
+            span, _p(scratch), _stream()))
+        _launches[0] += 1  # two kernels
+        return
+    if kernel == "tc" or (kernel is None and gated_attention_tc_takes(q, out, k_pool, head_dim, value_dim, max_q_len, gate, gate_kind)):
+        if not gated_attention_tc_takes(q, out, k_pool, head_dim, value_dim, max(max_q_len, GATED_TC_MIN_ROWS), gate, gate_kind):
+            raise KernelError("the tensor-core form takes bfloat16, pages of 64 and key and value sizes that are multiples of 16 up to 256")
+        lib = gated_attention_tc_library(head_dim, value_dim, v_pool is None)
+        _run(lib, lib.mb_gated_attention_tc(
+            _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pool), _p(values), _p(block_table), block_table.shape[1], _p(cu_q),
+            _p(kv_lens), _p(head_bias), _p(gate), gate_stride, GATE_KINDS[gate_kind], sequences, max_q_len, heads, kv_heads,
+            page_size, softmax, ctypes.c_float(scale), ctypes.c_float(slope_exponent), _stream()))
+        return
     lib = gated_attention_library()
     _run(lib, lib.mb_gated_attention_rows(
         _p(q), q.stride(0), _p(out), out.stride(0), _code(q.dtype), _p(k_pool), _p(values), values.shape[3], _p(block_table),
-        block_table.shape[1], _p(cu_q), _p(kv_lens), _p(head_bias), _p(gate), gate.stride(0) if gate is not None else 0,
-        GATE_KINDS[gate_kind], kv_lens.numel(), max_q_len, heads, kv_heads, head_dim, value_dim, page_size,
-        1 if weights == "softmax" else 0, ctypes.c_float(scale), ctypes.c_float(slope_exponent), _stream()))
+        block_table.shape[1], _p(cu_q), _p(kv_lens), _p(head_bias), _p(gate), gate_stride, GATE_KINDS[gate_kind], sequences,
+        max_q_len, heads, kv_heads, head_dim, value_dim, page_size, softmax, ctypes.c_float(scale), ctypes.c_float(slope_exponent),
+        _stream()))
 
 
 def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, heads: int, gate: Optional[torch.Tensor] = None) -> None:
@@ -619,6 +683,9 @@ def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, heads:
                                  gate.stride(0) if gate is not None else 0, x.shape[0], heads, n_in, n_out, _stream()))
 
 
+RETENTION_RUN = 64  # tokens of a run when a long step's recurrence is walked in runs
+
+
 def retention_library():
     return load_library("mb_retention", ["retention.cu"])
 
@@ -626,11 +693,14 @@ def retention_library():
 def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, positions: torch.Tensor,
                    cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int, decay: torch.Tensor,
                    key_scale: float, eps: float, state: torch.Tensor, slots: torch.Tensor, cu_q: torch.Tensor, heads: int,
-                   head_dim: int, value_dim: int, out: torch.Tensor, out_scale: float = 1.0) -> None:
+                   head_dim: int, value_dim: int, out: torch.Tensor, out_scale: float = 1.0, max_q_len: int = 1,
+                   run_length: Optional[int] = None) -> None:
     """Retention over the new tokens of every sequence: q and k rotated over their first `rotary_dim` coordinates
     (split-half pairs, float32 tables by position), k times key_scale; S = decay_h S + k v^T from the sequence's row of
     `state` (float32 [slots, heads, head_dim, value_dim], updated in place); o = S^T q; out = out_scale * o / rms(o) *
-    silu(g) per head, rms(o) = sqrt(mean(o^2) + eps).  q, k, v, g are column slices with one row stride."""
+    silu(g) per head, rms(o) = sqrt(mean(o^2) + eps).  q, k, v, g are column slices with one row stride.
+    `max_q_len`: the most new tokens of any sequence.  Beyond `run_length` tokens (None: RETENTION_RUN once a step brings
+    more than twice as many) the sequences are walked in runs of that many tokens at once, through scratch memory."""
     _cuda(q, k, v, g, positions, cos, sin, decay, state, slots, cu_q, out)
     _int32(positions, "positions")
     _int32(slots, "slots")
@@ -653,10 +723,18 @@ def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.T
         if cos.shape[-1] != rotary_dim // 2 or cos.shape != sin.shape or not cos.is_contiguous() or not sin.is_contiguous():
             raise KernelError(f"retention_scan: cos/sin tables must be contiguous [positions, {rotary_dim // 2}]")
     lib = retention_library()
+    if run_length is None:
+        run_length = RETENTION_RUN if max_q_len > 2 * RETENTION_RUN else 0
+    sequences = cu_q.numel() - 1
+    lib.mb_retention_scratch_floats.restype = ctypes.c_size_t
+    floats = lib.mb_retention_scratch_floats(sequences, heads, head_dim, value_dim, max_q_len, run_length)
+    scratch = torch.empty((floats,), dtype=torch.float32, device=q.device) if floats else None
     _run(lib, lib.mb_retention_scan(_p(q), _p(k), _p(v), _p(g), q.stride(0), _code(q.dtype), _p(positions), _p(cos), _p(sin),
                                     rotary_dim, _p(decay), ctypes.c_float(key_scale), ctypes.c_float(eps), _p(state), _p(slots),
-                                    _p(cu_q), cu_q.numel() - 1, heads, head_dim, value_dim, _p(out), out.stride(0),
-                                    ctypes.c_float(out_scale), _stream()))
+                                    _p(cu_q), sequences, heads, head_dim, value_dim, _p(out), out.stride(0),
+                                    ctypes.c_float(out_scale), max_q_len, run_length, _p(scratch), _stream()))
+    if floats:
+        _launches[0] += 2  # three kernels
 
 
 def gated_recurrence_library():

@@ -75,7 +75,7 @@ class RetentionMixer(SplitPart, Mixer):
         g = proj[:, at[3]:at[3] + self.v_width]
         ops.retention_scan(q, k, v, g, batch.positions, pos.cos if pos else None, pos.sin if pos else None,
                            pos.rotary_dim if pos else 0, self.decay, s.key_scale, s.eps, run.state, batch.slots, batch.cu_q,
-                           s.num_heads, s.head_dim, s.value_dim, mid, scale)
+                           s.num_heads, s.head_dim, s.value_dim, mid, scale, batch.max_q_len)
 
 
 register_part("mixer", "retention", RetentionMixer)

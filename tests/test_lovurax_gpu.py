@@ -60,7 +60,7 @@ def _pools(T, G, D, Dv, page_size, device, dtype, shuffle_seed=0):
     return k_pool, v_pool, order.to(torch.int32)[None, :].contiguous().to(device), mapping, positions.to(device)
 
 
-def _sigmoid_attend(q, k, v, gains, temp, bias, gate, scale, dtype, device, page_size=64, q_len=None):
+def _sigmoid_attend(q, k, v, gains, temp, bias, gate, scale, dtype, device, page_size=64, q_len=None, kernel=None):
     """norm_store then the sigmoid attention for the last `q_len` tokens of one sequence: float64 [q_len, H * Dv]."""
     from models_b200.kernels import ops
 
@@ -79,7 +79,7 @@ def _sigmoid_attend(q, k, v, gains, temp, bias, gate, scale, dtype, device, page
     ops.gated_attention(wide[T - q_len:, :a], out, k_pool, v_pool, table, cu_q, kv_lens, q_len, H, G, D, Dv, "sigmoid", scale, 8.0,
                         bias.float().to(device) if bias is not None else None,
                         gate[T - q_len:].to(dtype).to(device).contiguous() if gate is not None else None,
-                        "element" if gate is not None else None)
+                        "element" if gate is not None else None, kernel)
     return out.double().cpu()
 
 
@@ -106,7 +106,7 @@ def test_one_key_decides_the_sigmoid_attention(cuda_device, tokens, target, dtyp
     """All keys but one score far below zero (weights near 0); the key at `target` -- far back among hundreds, the
     first position, either side of a page border, the query's own position -- scores near zero, where the distance
     term and the head's bias move the weight, and carries a value found nowhere else."""
-    H, G, D, Dv = 4, 2, 16, 8
+    H, G, D, Dv = 4, 2, 16, 16
     gen = torch.Generator().manual_seed(tokens * 1000 + target)
     direction = torch.nn.functional.normalize(torch.randn(D, generator=gen, dtype=F), dim=0)
     q = torch.randn(tokens, H, D, generator=gen, dtype=F) * 0.1
@@ -121,8 +121,9 @@ def test_one_key_decides_the_sigmoid_attention(cuda_device, tokens, target, dtyp
     want = _plain_sigmoid_attend(q, k, v, None, (0.0, 1), bias, None, 1.0)[-1:]
     weight = want.reshape(H, Dv).mean(1) / 5.0  # (the steeper heads' weights of a far key are next to nothing)
     assert 0.05 < float(weight[-1]) < 0.95  # the flattest head's weight of the target is in the sigmoid's sensitive range
-    got = _sigmoid_attend(q, k, v, None, (0.0, 1), bias, None, 1.0, dtype, cuda_device, q_len=1)
-    assert scaled_error(got, want) < (2e-5 if dtype == torch.float32 else 2e-2)
+    for kernel in ("decode", "rows") + (("tc",) if dtype == torch.bfloat16 else ()):  # one token is a (short) prompt step too
+        got = _sigmoid_attend(q, k, v, None, (0.0, 1), bias, None, 1.0, dtype, cuda_device, q_len=1, kernel=kernel)
+        assert scaled_error(got, want) < (2e-5 if dtype == torch.float32 else 2e-2), kernel
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -141,9 +142,10 @@ def test_sigmoid_attention_sizes_norm_temperature_and_gate(cuda_device, heads, k
     bias = torch.randn(heads, generator=gen).to(F) - 2.0
     want = _plain_sigmoid_attend(q, k, v, gains, (0.6, every), bias, gate, 0.3)
     tol = 3e-5 if dtype == torch.float32 else 3e-2
-    for q_len in (T, 1, 37):
-        got = _sigmoid_attend(q, k, v, gains, (0.6, every), bias, gate, 0.3, dtype, cuda_device, page_size=page, q_len=q_len)
-        assert scaled_error(got, want[T - q_len:]) < tol, q_len
+    for q_len, kernel in ((T, None), (1, None), (37, None), (T, "rows"), (1, "rows")):
+        # (None: the tensor-core form for bfloat16 prompts of sizes it takes, the split-key form for one token)
+        got = _sigmoid_attend(q, k, v, gains, (0.6, every), bias, gate, 0.3, dtype, cuda_device, page_size=page, q_len=q_len, kernel=kernel)
+        assert scaled_error(got, want[T - q_len:]) < tol, (q_len, kernel)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -193,6 +195,43 @@ def test_one_latent_row_decides_the_softmax(cuda_device, tokens, target, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,rank,tokens", [(5, 48, 200), (16, 256, 330), (2, 40, 70), (9, 64, 129)])
+def test_softmax_over_shared_rows_in_every_form(cuda_device, heads, rank, tokens, dtype):
+    """All heads read the same cached rows as keys and as values; prompts (the tensor-core form where it takes the
+    sizes), a portion of a prompt, and one token with the keys cut into runs; a gate per head."""
+    from models_b200.kernels import ops
+
+    gen = torch.Generator().manual_seed(rank + tokens)
+    rows = _rounded(torch.randn(tokens, rank, generator=gen, dtype=F), dtype)
+    q = _rounded(torch.randn(tokens, heads, rank, generator=gen, dtype=F) * 0.5, dtype)
+    gate = _rounded(torch.randn(tokens, heads, generator=gen, dtype=F), dtype)
+    k_pool, _, table, mapping, positions = _pools(tokens, 1, rank, 0, 64, cuda_device, dtype, shuffle_seed=5)
+    ops.norm_store(None, rows.to(dtype).to(cuda_device), None, positions, None, None, 1e-6, 0.0, 1, k_pool, None, mapping, 0, 1, rank, 0)
+    visible = torch.ones(tokens, tokens).tril().bool()
+    want = []
+    for h in range(heads):
+        score = torch.where(visible, 0.2 * q[:, h] @ rows.T, torch.full((), -math.inf, dtype=F))
+        want.append(torch.softmax(score, -1) @ rows * pl.sigmoid(gate[:, h:h + 1]))
+    want = torch.stack(want, dim=1).reshape(tokens, -1)
+    kv_lens = torch.tensor([tokens], dtype=torch.int32, device=cuda_device)
+    for q_len, kernel in ((tokens, None), (33, None), (1, None), (tokens, "rows"), (1, "rows")):
+        out = torch.empty((q_len, heads * rank), dtype=dtype, device=cuda_device)
+        cu_q = torch.tensor([0, q_len], dtype=torch.int32, device=cuda_device)
+        ops.gated_attention(q[tokens - q_len:].reshape(q_len, -1).to(dtype).to(cuda_device), out, k_pool, None, table, cu_q, kv_lens, q_len,
+                            heads, 1, rank, rank, "softmax", 0.2, 0.0, None, gate[tokens - q_len:].to(dtype).to(cuda_device).contiguous(),
+                            "head", kernel)
+        assert scaled_error(out, want[tokens - q_len:]) < (2e-5 if dtype == torch.float32 else 2e-2), (q_len, kernel)
+
+
+def test_decode_runs_cover_the_page_table():
+    from models_b200.kernels import ops
+
+    for sequences, heads, kv_heads, pages in ((1, 4, 2, 1), (1, 16, 1, 512), (8, 16, 4, 24), (64, 32, 8, 3), (2, 3, 3, 100)):
+        runs, span = ops.gated_decode_runs(sequences, heads, kv_heads, pages)
+        assert runs >= 1 and span >= 1 and runs * span >= pages and (runs - 1) * span < pages and runs <= 64
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,n_in,n_out,tokens", [(1, 8, 8, 1), (3, 12, 40, 17), (5, 40, 6, 100), (4, 64, 128, 33)])
 def test_one_small_matrix_per_head(cuda_device, heads, n_in, n_out, tokens, dtype):
     from models_b200.kernels import ops
@@ -228,12 +267,14 @@ def _plain_retention(q, k, v, g, decay, rot, first_position, eps, start=None):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("run_length", [0, 16, 7])
 @pytest.mark.parametrize("heads,dim,vdim,rot,decay", [(2, 16, 24, (8, 10000.0), [0.9, 0.999]), (1, 32, 32, (32, 50.0), [1.0]),
                                                       (3, 10, 6, (0, 1.0), [0.5, 0.0, 0.97]), (2, 64, 128, (32, 1e6), [0.99, 0.95])])
-def test_retention_ragged_carried_and_rotated(cuda_device, heads, dim, vdim, rot, decay, dtype):
+def test_retention_ragged_carried_and_rotated(cuda_device, heads, dim, vdim, rot, decay, run_length, dtype):
     """Sequences of unequal lengths in one call, then one more token for each (the state is carried in float32 between
     calls, positions go on from where the sequence stands, far from zero for one of them), rows of unused slots
-    untouched; decays of 0 (no memory), 1 (nothing forgotten) and in between."""
+    untouched; decays of 0 (no memory), 1 (nothing forgotten) and in between; the sequences walked whole, and in runs of
+    16 and of 7 tokens at once (the last run of a sequence is shorter, some sequences have one run, some runs are empty)."""
     from models_b200.kernels import ops
     from models_b200.parts.rope import RotaryEmbedding
     from models_b200.config.specs import RopeSpec
@@ -267,14 +308,15 @@ def test_retention_ragged_carried_and_rotated(cuda_device, heads, dim, vdim, rot
         out = torch.empty((total, heads * vdim), dtype=dtype, device=device)
         ops.retention_scan(dev[:, :a], dev[:, a:b], dev[:, b:c], dev[:, c:], positions, tables.cos if tables else None,
                            tables.sin if tables else None, rot[0], torch.tensor(decay, dtype=torch.float32, device=device),
-                           dim ** -0.5, 1e-6, state, slots, torch.tensor(cu, dtype=torch.int32, device=device), heads, dim, vdim, out)
+                           dim ** -0.5, 1e-6, state, slots, torch.tensor(cu, dtype=torch.int32, device=device), heads, dim, vdim, out,
+                           1.0, max(counts), run_length)
         for i, n in enumerate(counts):
             rows = proj[cu[i]:cu[i + 1]]
             want, plain_state[i] = _plain_retention(rows[:, :a].view(n, heads, dim), rows[:, a:b].view(n, heads, dim),
                                                     rows[:, b:c].view(n, heads, vdim), rows[:, c:], decay, rot, starts[i], 1e-6,
                                                     plain_state[i])
             assert scaled_error(out[cu[i]:cu[i + 1]], want) < tol, (call, i)
-            assert scaled_error(state[int(slots[i])], plain_state[i]) < (1e-5 if dtype == torch.float32 else 1e-5), (call, i)
+            assert scaled_error(state[int(slots[i])], plain_state[i]) < 1e-5, (call, i)
             starts[i] += n
     assert bool((state[5] == 7.0).all()) and bool((state[3] == 0.0).all())
 
