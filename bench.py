@@ -447,15 +447,157 @@ def design_kernels(z, peak, prompt=2048, batch=8, context=1536):
     return out
 
 
+# --design lovurax: the Lovurax decoder (sigmoid attention, retention and latent attention layers in turn, gated
+# residuals, an xIELU feed-forward) beside a Llama of equal size, the same way.
+
+LOVURAX_SIZES = {
+    # width, layers (attention, retention, attention, latent attention in turn), heads, key/value heads of the attention,
+    # key size, value size, rank of the latent rows, ff
+    "s": dict(width=1024, layers=8, heads=8, kv_heads=2, dim=64, vdim=128, rank=256, ff=2048),
+    "m": dict(width=2048, layers=16, heads=16, kv_heads=4, dim=64, vdim=128, rank=256, ff=4096),
+}
+LOVURAX_ORDER = ("attention", "retention", "attention", "latent_attention")
+
+
+def lovurax_config(z):
+    H, D, DV = z["heads"], z["dim"], z["vdim"]
+    mixers = {
+        "attention": {"heads": H, "kv_heads": z["kv_heads"], "dim": D, "vdim": DV, "scale": D ** -0.5, "q_temp": {"coef": 0.5, "every": 256}},
+        "retention": {"heads": H, "dim": D, "vdim": DV, "decay": [1.0 - 2.0 ** (-5 - 3 * h / max(1, H - 1)) for h in range(H)],
+                      "rot": {"dims": D // 2, "base": 500000.0}},
+        "latent_attention": {"heads": H, "dim": D, "vdim": DV, "kv_rank": z["rank"], "scale": D ** -0.5},
+    }
+    layers = [{"type": LOVURAX_ORDER[i % 4], "mixer": mixers[LOVURAX_ORDER[i % 4]], "mlp": {"kind": "dense", "ff": z["ff"]}}
+              for i in range(z["layers"])]
+    return {"architecture": "Lovurax", "vocab": DESIGN_VOCAB, "width": z["width"], "norm": {"eps": 1e-6}, "logit_scale": 1.0, "layers": layers}
+
+
+def lovurax_layer_params(z):
+    """Matrix parameters of a layer, averaged over the four layers of a turn."""
+    w, h, g, d, dv, r = (z[k] for k in ("width", "heads", "kv_heads", "dim", "vdim", "rank"))
+    mixer = {"attention": w * (h * d + g * d + g * dv + h * dv) + h * dv * w,
+             "retention": w * (2 * h * d + 2 * h * dv) + h * dv * w,
+             "latent_attention": w * (h * d + r + h) + r * (h * d + h * dv) + h * dv * w}
+    return sum(mixer[kind] for kind in LOVURAX_ORDER) // 4 + 2 * w * w + 2 * w * z["ff"]
+
+
+def llama_of_equal_size(z, layer_params):
+    """A Llama with the same width, layers, heads and key/value heads, heads of 128 (queries and values as wide as the
+    design's values), and the feed-forward width that makes a layer's parameters equal (a multiple of 256)."""
+    w, h, g, hd = z["width"], z["heads"], z["kv_heads"], 128
+    attention = w * (h * hd + 2 * g * hd) + h * hd * w
+    inter = max(256, round((layer_params - attention) / (3 * w) / 256) * 256)
+    return dict(LLAMA_3_2_1B, num_hidden_layers=z["layers"], hidden_size=w, num_attention_heads=h, num_key_value_heads=g,
+                head_dim=hd, intermediate_size=inter, vocab_size=DESIGN_VOCAB, rope_scaling=None,
+                tie_word_embeddings=False, max_position_embeddings=8192)
+
+
+def lovurax_kernels(z, peak, prompt=2048, batch=8, context=1536):
+    """The design's kernels alone beside the like kernels of the other models at equal sizes, each with its fraction
+    of the measured peak that bounds it."""
+    import torch
+
+    from models_b200.kernels import ops
+
+    dev, bf = "cuda", torch.bfloat16
+    H, G, D, DV, R, W = (z[k] for k in ("heads", "kv_heads", "dim", "vdim", "rank", "width"))
+    page = 64
+    out = {}
+
+    def paged(sequences, length, kv_heads, key, value):
+        pages = sequences * (-(-length // page))
+        k_pool = torch.randn((pages + 1, kv_heads, page, key), device=dev).to(bf)
+        v_pool = torch.randn((pages + 1, kv_heads, page, value), device=dev).to(bf) if value else None
+        table = (torch.arange(pages, dtype=torch.int32, device=dev) + 1).reshape(sequences, -1).contiguous()
+        return k_pool, v_pool, table
+
+    def rated(us, flops=None, moved=None):
+        if flops is not None:
+            return {"us": us, "tflops": flops / us / 1e6, "frac_of_bf16_peak": flops / us / 1e6 / peak["bf16_tflops"]}
+        return {"us": us, "gbs": moved / us / 1e3, "frac_of_hbm_peak": moved / us / 1e3 / peak["hbm_gbs"]}
+
+    hd = 128
+    for name, rows, cu_q, lengths, q_len in (("prompt", prompt, [0, prompt], [prompt], prompt),
+                                             ("decode", batch, list(range(batch + 1)), [context] * batch, 1)):
+        sequences = len(lengths)
+        cu = torch.tensor(cu_q, dtype=torch.int32, device=dev)
+        kv = torch.tensor(lengths, dtype=torch.int32, device=dev)
+        pairs = sum(sum(range(n - q_len + 1, n + 1)) for n in lengths)  # (query, key) pairs of a head
+        # sigmoid attention: keys of D, values of DV, a gate per element
+        k_pool, v_pool, table = paged(sequences, lengths[0], G, D, DV)
+        q, o = torch.randn((rows, H * D), device=dev).to(bf), torch.empty((rows, H * DV), dtype=bf, device=dev)
+        gate, bias = torch.randn((rows, H * DV), device=dev).to(bf), torch.zeros(H, device=dev)
+        us = time_kernel(lambda: ops.gated_attention(q, o, k_pool, v_pool, table, cu, kv, q_len, H, G, D, DV, "sigmoid", D ** -0.5, 8.0,
+                                                     bias, gate, "element"))
+        out[f"{name}_sigmoid_attention"] = rated(us, flops=pairs * H * (2 * D + 2 * DV)) if q_len > 1 else \
+            rated(us, moved=sum(lengths) * G * (D + DV) * 2)
+        # latent attention: every head reads the rows of R as key and as value; the two small products per head around it
+        c_pool, _, table = paged(sequences, lengths[0], 1, R, 0)
+        ql, ol = torch.randn((rows, H * R), device=dev).to(bf) * 0.1, torch.empty((rows, H * R), dtype=bf, device=dev)
+        us = time_kernel(lambda: ops.gated_attention(ql, ol, c_pool, None, table, cu, kv, q_len, H, 1, R, R, "softmax", D ** -0.5))
+        out[f"{name}_latent_attention"] = rated(us, flops=pairs * H * 4 * R) if q_len > 1 else rated(us, moved=sum(lengths) * R * 2)
+        into, back = torch.randn((H, R, D), device=dev).to(bf), torch.randn((H, DV, R), device=dev).to(bf)
+        q_small, o_small = torch.randn((rows, H * D), device=dev).to(bf), torch.empty((rows, H * DV), dtype=bf, device=dev)
+        us = time_kernel(lambda: (ops.head_linear(q_small, into, ql, H), ops.head_linear(ol, back, o_small, H)))
+        out[f"{name}_latent_head_products"] = rated(us, flops=rows * H * 2 * R * (D + DV)) if q_len > 1 else \
+            rated(us, moved=H * R * (D + DV) * 2)
+        # the like Llama kernel: heads of 128
+        k2, v2, table = paged(sequences, lengths[0], G, hd, hd)
+        q2, o2 = torch.randn((rows, H * hd), device=dev).to(bf), torch.empty((rows, H * hd), dtype=bf, device=dev)
+        if q_len > 1:
+            us = time_kernel(lambda: ops.prefill_attention(q2, o2, k2, v2, table, cu, kv, q_len, H, G, hd, None, hd ** -0.5))
+            out[f"{name}_attention_llama"] = rated(us, flops=pairs * H * 4 * hd)
+        else:
+            splits = ops.decode_splits(sequences, H, G, hd, lengths[0], None, ops.multiprocessors(torch.device(dev)))
+            us = time_kernel(lambda: ops.decode_attention(q2, o2, k2, v2, table, cu, kv, H, G, hd, None, hd ** -0.5, splits))
+            out[f"{name}_attention_llama"] = rated(us, moved=sum(lengths) * G * 2 * hd * 2)
+        # retention beside the other recurrence of the package (minGRU over as many channels as the state has columns)
+        state = torch.zeros((sequences + 1, H, D, DV), dtype=torch.float32, device=dev)
+        proj = torch.randn((rows, 2 * H * D + 2 * H * DV), device=dev).to(bf)
+        a, b, c = H * D, 2 * H * D, 2 * H * D + H * DV
+        y = torch.empty((rows, H * DV), dtype=bf, device=dev)
+        positions = torch.cat([torch.arange(n - q_len, n) for n in lengths]).to(torch.int32).to(dev)
+        tables = torch.rand((max(lengths), D // 4), device=dev)
+        decay = torch.full((H,), 0.99, device=dev)
+        slots = torch.arange(sequences, dtype=torch.int32, device=dev)
+        us = time_kernel(lambda: ops.retention_scan(proj[:, :a], proj[:, a:b], proj[:, b:c], proj[:, c:], positions, tables, tables, D // 2,
+                                                    decay, D ** -0.5, 1e-6, state, slots, cu, H, D, DV, y, 1.0, q_len))
+        # what must move: the projections and results once, the state in and out; the arithmetic: 2 x 2 D DV per token and head
+        moved = rows * (2 * H * D + 3 * H * DV) * 2 + sequences * H * D * DV * 8
+        out[f"{name}_retention"] = dict(rated(us, moved=moved), fp32_tflops=rows * H * 4 * D * DV / us / 1e6)
+        width = H * DV
+        gru_state = torch.zeros((sequences + 1, width), dtype=torch.float32, device=dev)
+        gp, gy = torch.randn((rows, 3 * width), device=dev).to(bf), torch.empty((rows, width), dtype=bf, device=dev)
+        zb = torch.zeros(width, device=dev)
+        us = time_kernel(lambda: ops.mingru_scan(gp[:, :width], gp[:, width:2 * width], gp[:, 2 * width:], zb, zb, gru_state, slots, cu, q_len, gy))
+        out[f"{name}_recurrence_kabanex"] = rated(us, moved=rows * width * 2 * 4 + sequences * width * 8)
+    # element-wise: the gated residual add beside the plain one, the activation beside the gated one of Llama
+    x, delta = torch.randn((prompt, W), device=dev), torch.randn((prompt, W), device=dev)
+    gate, bias = torch.randn((prompt, W), device=dev).to(bf), torch.zeros(W, device=dev)
+    out["prompt_gated_residual_add"] = rated(time_kernel(lambda: ops.gated_residual_add(x, gate, bias, delta)), moved=prompt * W * 14)
+    out["prompt_residual_add_llama"] = rated(time_kernel(lambda: ops.residual_add(x, delta)), moved=prompt * W * 12)
+    up, mid = torch.randn((prompt, z["ff"]), device=dev).to(bf), torch.empty((prompt, z["ff"]), dtype=bf, device=dev)
+    out["prompt_xielu"] = rated(time_kernel(lambda: ops.xielu(up, mid, 0.7, 1.2)), moved=prompt * z["ff"] * 4)
+    gate_up = torch.randn((prompt, 2 * z["ff"]), device=dev).to(bf)
+    out["prompt_swiglu_llama"] = rated(time_kernel(lambda: ops.swiglu(gate_up)), moved=prompt * z["ff"] * 6)
+    return out
+
+
 def design_run(args) -> int:
     import torch
 
     peak = peaks()
     batch, prompt, prefill_tokens, steps, warmup = 8, 512, 2048, args.steps or 64, max(args.warmup, 3)
+    if args.design == "kabanex":
+        title, all_sizes, make, params, beside, alone = "Kabanex", DESIGN_SIZES, kabanex_config, kabanex_layer_params, \
+            (lambda z: llama_like(z)), design_kernels
+    else:
+        title, all_sizes, make, params, beside, alone = "Lovurax", LOVURAX_SIZES, lovurax_config, lovurax_layer_params, \
+            (lambda z: llama_of_equal_size(z, lovurax_layer_params(z))), lovurax_kernels
     sizes = {}
-    for name, z in DESIGN_SIZES.items():
-        entry = {"sizes": z, "layer_params": kabanex_layer_params(z)}
-        for arch, config in (("kabanex", kabanex_config(z)), ("llama", llama_like(z))):
+    for name, z in all_sizes.items():
+        entry = {"sizes": z, "layer_params": params(z)}
+        for arch, config in ((args.design, make(z)), ("llama", beside(z))):
             model = make_model(config, batch, prefill_tokens + 64)
             ms = device_prefill(model, prefill_tokens)
             run = device_decode(model, batch, steps, warmup, prompt=prompt)
@@ -467,9 +609,9 @@ def design_run(args) -> int:
             model.close()
             del model
             torch.cuda.empty_cache()
-        entry["kernels_alone"] = design_kernels(z, peak)
+        entry["kernels_alone"] = alone(z, peak)
         sizes[name] = entry
-    print(json.dumps({"design": "Kabanex", "beside": "LlamaForCausalLM of equal size", "dtype": "bf16", "gpu": torch.cuda.get_device_name(0),
+    print(json.dumps({"design": title, "beside": "LlamaForCausalLM of equal size", "dtype": "bf16", "gpu": torch.cuda.get_device_name(0),
                       "data": "synthetic: seeded uniform-random token ids, random weights N(0, 0.02)",
                       "workload": {"prefill_tokens": prefill_tokens, "decode_batch": batch, "decode_prompt": prompt, "decode_steps": steps,
                                    "warmup": warmup, "vocab": DESIGN_VOCAB},
@@ -492,7 +634,7 @@ def main() -> int:
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 decode points and the prefill")
     parser.add_argument("--only-prefill", action="store_true",
                         help="run the workload's prefill alone and print its figures (for profiling)")
-    parser.add_argument("--design", default=None, choices=["kabanex"],
+    parser.add_argument("--design", default=None, choices=["kabanex", "lovurax"],
                         help="instead of the default run: this design beside a Llama of equal size (prefill, decode, its kernels alone)")
     args = parser.parse_args()
     if args.design and args.impl == "ours":

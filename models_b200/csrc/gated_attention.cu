@@ -250,14 +250,19 @@ gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __
         if (visible) {
             const T* k_row = k_pool + (base + lane) * head_dim;
             if (vector_ok) {
+#pragma unroll 2
                 for (int d = 0; d < head_dim; d += 8) {
                     float kv[8];
                     load8(k_row + d, kv);
 #pragma unroll
                     for (int g = 0; g < kGroup; ++g)
                         if (g < count) {
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) score[g] = fmaf(q_shared[g * head_dim + d + i], kv[i], score[g]);
+                            const float4 qa = *reinterpret_cast<const float4*>(q_shared + g * head_dim + d);
+                            const float4 qb = *reinterpret_cast<const float4*>(q_shared + g * head_dim + d + 4);
+                            score[g] = fmaf(qa.x, kv[0], score[g]), score[g] = fmaf(qa.y, kv[1], score[g]);
+                            score[g] = fmaf(qa.z, kv[2], score[g]), score[g] = fmaf(qa.w, kv[3], score[g]);
+                            score[g] = fmaf(qb.x, kv[4], score[g]), score[g] = fmaf(qb.y, kv[5], score[g]);
+                            score[g] = fmaf(qb.z, kv[6], score[g]), score[g] = fmaf(qb.w, kv[7], score[g]);
                         }
                 }
             } else {
@@ -285,17 +290,26 @@ gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __
                 weight[g] = visible ? sigmoid(z) : 0.0f;
             }
         }
+        // the values of kAhead keys are asked for before the first is used (a key beyond the run's end has weight 0 and
+        // reads the run's last row again)
+        constexpr int kAhead = kAcc <= 4 ? 8 : 4;
         const int last = min(31, end - 1 - chunk);
-        for (int jj = 0; jj <= last; ++jj) {
-            const T* v_row = v_pool + (base + jj) * v_width;
-            float value[kAcc];
+        for (int j0 = 0; j0 <= last; j0 += kAhead) {
+            float value[kAhead][kAcc];
 #pragma unroll
-            for (int i = 0; i < kAcc; ++i) value[i] = lane + 32 * i < value_dim ? Num<T>::load(v_row + lane + 32 * i) : 0.0f;
+            for (int u = 0; u < kAhead; ++u) {
+                const T* v_row = v_pool + (base + min(j0 + u, last)) * v_width;
 #pragma unroll
-            for (int g = 0; g < kGroup; ++g) {
-                const float w = __shfl_sync(0xffffffffu, weight[g], jj);
+                for (int i = 0; i < kAcc; ++i) value[u][i] = lane + 32 * i < value_dim ? Num<T>::load(v_row + lane + 32 * i) : 0.0f;
+            }
 #pragma unroll
-                for (int i = 0; i < kAcc; ++i) acc[g][i] = fmaf(w, value[i], acc[g][i]);
+            for (int u = 0; u < kAhead; ++u) {
+#pragma unroll
+                for (int g = 0; g < kGroup; ++g) {
+                    const float w = __shfl_sync(0xffffffffu, weight[g], (j0 + u) & 31);
+#pragma unroll
+                    for (int i = 0; i < kAcc; ++i) acc[g][i] = fmaf(w, value[u][i], acc[g][i]);
+                }
             }
         }
     }
@@ -365,9 +379,12 @@ __global__ void gated_attention_combine_kernel(const float* __restrict__ partial
 }
 
 // out[t, h * n_out + n] = gate * sum_k in[t, h * n_in + k] * w[(h * n_out + n) * n_in + k]: one small matrix per head,
-// rows of n_in weights; gate: sigmoid of gate[t, h] when given.  grid (ceil(tokens / kRows), heads); block 128.
-// shared: kRows * n_in floats.
+// rows of n_in weights; gate: sigmoid of gate[t, h] when given.
+// Plain arithmetic: grid (ceil(tokens / 16), heads, ceil(n_out / 32)); block 128.  A warp takes 8 of the block's 32
+// outputs in turn: its lanes walk a weight row together (neighbouring lanes read neighbouring weights), each with a sum
+// per token, and the sums meet by shuffles.  shared: 16 * n_in floats.
 constexpr int kHeadRows = 16;
+constexpr int kHeadOutputs = 32;
 
 template <typename T>
 __global__ void head_linear_kernel(const T* __restrict__ in, int in_stride, const T* __restrict__ w, T* __restrict__ out,
@@ -377,31 +394,138 @@ __global__ void head_linear_kernel(const T* __restrict__ in, int in_stride, cons
     extern __shared__ float rows_shared[];  // [kHeadRows][n_in]
     const int head = blockIdx.y, first = blockIdx.x * kHeadRows;
     const int rows = min(kHeadRows, tokens - first);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int item = threadIdx.x; item < kHeadRows * n_in; item += blockDim.x) {
         const int r = item / n_in, k = item % n_in;
         rows_shared[item] = r < rows ? Num<T>::load(in + (size_t)(first + r) * in_stride + (size_t)head * n_in + k) : 0.0f;
     }
     __syncthreads();
-    for (int n = threadIdx.x; n < n_out; n += blockDim.x) {
+    for (int i = 0; i < kHeadOutputs / 4; ++i) {
+        const int n = blockIdx.z * kHeadOutputs + warp * (kHeadOutputs / 4) + i;
+        if (n >= n_out) break;
         const T* w_row = w + ((size_t)head * n_out + n) * n_in;
         float acc[kHeadRows];
 #pragma unroll
         for (int r = 0; r < kHeadRows; ++r) acc[r] = 0.0f;
-        for (int k = 0; k < n_in; ++k) {
+        for (int k = lane; k < n_in; k += 32) {
             const float weight = Num<T>::load(w_row + k);
 #pragma unroll
             for (int r = 0; r < kHeadRows; ++r) acc[r] = fmaf(rows_shared[r * n_in + k], weight, acc[r]);
         }
+        // lane r ends up with token r's sum (every sum is added over the lanes in the same order)
+        float mine = 0.0f;
 #pragma unroll
         for (int r = 0; r < kHeadRows; ++r) {
-            if (r < rows) {
-                float value = acc[r];
-                if (gate != nullptr) value *= sigmoid(Num<T>::load(gate + (size_t)(first + r) * gate_stride + head));
-                Num<T>::store(out + (size_t)(first + r) * out_stride + (size_t)head * n_out + n, value);
-            }
+            const float total = warp_sum(acc[r]);
+            if (lane == r) mine = total;
+        }
+        if (lane < rows) {
+            if (gate != nullptr) mine *= sigmoid(Num<T>::load(gate + (size_t)(first + lane) * gate_stride + head));
+            Num<T>::store(out + (size_t)(first + lane) * out_stride + (size_t)head * n_out + n, mine);
         }
     }
 }
+
+// The same product on the tensor cores, for bfloat16 steps of many tokens: grid (ceil(tokens / 64), heads); block 128,
+// a warp 16 tokens.  The head's 64 x n_in activations and, 64 rows at a time, its weights pass through shared memory
+// (cp.async, two stages); m16n8k16 products with float sums.  n_in and n_out are multiples of 16.
+namespace tc {
+
+using bf16 = __nv_bfloat16;
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int kTile = 64;
+
+__global__ void __launch_bounds__(128)
+head_linear_tc_kernel(const bf16* __restrict__ in, int in_stride, const bf16* __restrict__ w, bf16* __restrict__ out, int out_stride,
+                      const bf16* __restrict__ gate, int gate_stride, int tokens, int n_in, int n_out) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    extern __shared__ __align__(16) unsigned char tc_smem[];
+    const int row_bytes = n_in * 2 + 16, tile_bytes = kTile * row_bytes, pieces = n_in / 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, group_id = lane >> 2, tid4 = lane & 3;
+    const int head = blockIdx.y, first = blockIdx.x * kTile;
+    const int valid = min(kTile, tokens - first);
+    const bf16* w_head = w + (size_t)head * n_out * n_in;
+    const uint32_t x_tile = smem_u32(tc_smem), w_tiles = x_tile + tile_bytes;
+    const int chunks = (n_out + kTile - 1) / kTile;
+    auto load_weights = [&](int chunk, int stage) {
+        const int rows = min(kTile, n_out - chunk * kTile);  // (a multiple of 16; rows beyond it are never read)
+        for (int i = threadIdx.x; i < rows * pieces; i += 128) {
+            const int row = i / pieces, piece = i % pieces;
+            cp_async16(w_tiles + stage * tile_bytes + row * row_bytes + piece * 16, w_head + (size_t)(chunk * kTile + row) * n_in + piece * 8);
+        }
+    };
+    load_weights(0, 0);
+    cp_async_commit();
+    for (int i = threadIdx.x; i < kTile * pieces; i += 128) {
+        const int row = i / pieces, piece = i % pieces;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (row < valid) v = *reinterpret_cast<const uint4*>(in + (size_t)(first + row) * in_stride + (size_t)head * n_in + piece * 8);
+        *reinterpret_cast<uint4*>(tc_smem + row * row_bytes + piece * 16) = v;
+    }
+    const uint32_t a_rows = x_tile + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * row_bytes + (lane >> 4) * 16;
+    float factor[2] = {1.0f, 1.0f};
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = warp * 16 + group_id + 8 * r;
+        if (gate != nullptr && row < valid) factor[r] = sigmoid(__bfloat162float(gate[(size_t)(first + row) * gate_stride + head]));
+    }
+    for (int chunk = 0; chunk < chunks; ++chunk) {
+        const int stage = chunk & 1;
+        if (chunk + 1 < chunks) {
+            load_weights(chunk + 1, stage ^ 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int rows = min(kTile, n_out - chunk * kTile);
+        const uint32_t w_tile = w_tiles + stage * tile_bytes;
+        for (int part = 0; part * 16 < rows; ++part) {
+            float s[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
+            const int w_row = part * 16 + (lane & 7) + ((lane >> 4) & 1) * 8;
+            for (int ks = 0; ks < n_in / 16; ++ks) {
+                uint32_t a[4], b[4];
+                ldmatrix_x4(a, a_rows + ks * 32);
+                ldmatrix_x4(b, w_tile + w_row * row_bytes + (ks * 2 + ((lane >> 3) & 1)) * 16);
+                mma_bf16(s[0], a, b[0], b[1]);
+                mma_bf16(s[1], a, b[2], b[3]);
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int row = warp * 16 + group_id + 8 * r;
+                if (row >= valid) continue;
+                bf16* dst = out + (size_t)(first + row) * out_stride + (size_t)head * n_out + chunk * kTile + part * 16 + tid4 * 2;
+                *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(s[0][2 * r] * factor[r], s[0][2 * r + 1] * factor[r]);
+                *reinterpret_cast<__nv_bfloat162*>(dst + 8) = __floats2bfloat162_rn(s[1][2 * r] * factor[r], s[1][2 * r + 1] * factor[r]);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace tc
 
 template <typename T>
 int launch_norm_store(void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, const int* positions,
@@ -562,14 +686,30 @@ MB_EXPORT int mb_gated_attention_decode(const void* q, int q_stride, void* out, 
     return status ? status : check_launch("gated_attention_decode");
 }
 
+// tensor_cores != 0 asks for the tensor-core form where it applies (bfloat16, n_in and n_out multiples of 16, rows that
+// start on 16 bytes (in) and 4 bytes (out), at least 16 tokens).
 MB_EXPORT int mb_head_linear(const void* in, int in_stride, const void* w, void* out, int out_stride, int dtype, const void* gate,
-                             int gate_stride, int tokens, int heads, int n_in, int n_out, cudaStream_t stream) {
+                             int gate_stride, int tokens, int heads, int n_in, int n_out, int tensor_cores, cudaStream_t stream) {
     if (tokens <= 0 || heads <= 0) return 0;
     if (n_in <= 0 || n_out <= 0) return fail("head_linear: sizes must be positive, got %d -> %d", n_in, n_out);
     if (heads > 65535) return fail("head_linear: %d heads exceed the grid limit 65535", heads);
+    if (tensor_cores && dtype == MB_BF16 && tokens >= 16 && n_in % 16 == 0 && n_out % 16 == 0 && n_in <= 512 && in_stride % 8 == 0 &&
+        out_stride % 2 == 0 && !((uintptr_t)in & 15) && !((uintptr_t)w & 15) && !((uintptr_t)out & 3)) {
+        const size_t smem = 3 * (size_t)tc::kTile * (n_in * 2 + 16);
+        static int reserved = 0;
+        if ((int)smem > reserved) {
+            cudaError_t status = cudaFuncSetAttribute(tc::head_linear_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (status != cudaSuccess) return fail("head_linear: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(status));
+            reserved = (int)smem;
+        }
+        MB_LAUNCH("head_linear_tc", tc::head_linear_tc_kernel, dim3((tokens + tc::kTile - 1) / tc::kTile, heads), dim3(128), smem, stream, true,
+                  (const __nv_bfloat16*)in, in_stride, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)gate,
+                  gate_stride, tokens, n_in, n_out);
+        return check_launch("head_linear_tc");
+    }
     const size_t smem = (size_t)kHeadRows * n_in * sizeof(float);
     if (smem > 200 * 1024) return fail("head_linear: %d inputs per head exceed a block's shared memory", n_in);
-    const dim3 grid((tokens + kHeadRows - 1) / kHeadRows, heads);
+    const dim3 grid((tokens + kHeadRows - 1) / kHeadRows, heads, (n_out + kHeadOutputs - 1) / kHeadOutputs);
     if (dtype == MB_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(head_linear_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         MB_LAUNCH("head_linear", head_linear_kernel<float>, dim3(grid), dim3(128), smem, stream, true, (const float*)in, in_stride,

@@ -28,11 +28,13 @@ constexpr int kWhole = 0;      // one run: from the stored state, results writte
 constexpr int kSummarise = 1;  // a run from a zero state, no results: what it adds goes to scratch [run]
 constexpr int kEmit = 2;       // a run from its starting state in scratch [run], results written
 
-// grid (heads, sequences, runs); block: value_dim rounded up to a multiple of 32 (at most 1024).
-// shared: S [head_dim * value_dim], q [2][head_dim], k [2][head_dim], 32 floats for sums.
+// grid (heads, sequences, runs); block: value_dim rounded up to a multiple of 32 (at most 1024; 256 with kDim > 0).
+// kDim > 0: head_dim is kDim and a thread keeps its column of S in registers (a column in shared memory costs two
+// shared-memory accesses per product, which is what bounds the kernel then); kDim 0: any head_dim, columns in shared memory.
+// shared: q [2][head_dim], k [2][head_dim], 32 floats for sums, and with kDim 0 S [head_dim * value_dim].
 // scratch: [sequence][head][run][head_dim * value_dim] floats.
-template <typename T, int kMode>
-__global__ void __launch_bounds__(1024)
+template <typename T, int kMode, int kDim>
+__global__ void __launch_bounds__(kDim > 0 ? 256 : 1024)
 retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ g,
                       int in_stride, const int* __restrict__ positions, const float* __restrict__ cos_table,
                       const float* __restrict__ sin_table, int rotary_dim, const float* __restrict__ decay, float key_scale,
@@ -48,17 +50,22 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
     const int first = sequence_first + run * run_length;
     const int count = kMode == kWhole ? sequence_count : min(run_length, sequence_count - run * run_length);
     if (count <= 0) return;  // the whole block leaves
-    float* S = shared;
-    float* qk = S + (size_t)head_dim * value_dim;  // [2 buffers][q | k][head_dim]
+    float* qk = shared;  // [2 buffers][q | k][head_dim]
     float* sums = qk + 4 * head_dim;
+    float* S = sums + 32;  // (kDim 0 only)
+    float column_kept[kDim > 0 ? kDim : 1];
     const int j = threadIdx.x;
     const bool live = j < value_dim;
     const int half = rotary_dim / 2;
     const float a = decay[head];
     float* stored = kMode == kWhole ? state + ((size_t)slots[seq] * heads + head) * head_dim * value_dim
                                     : scratch + (((size_t)seq * heads + head) * gridDim.z + run) * head_dim * value_dim;
-    if (live)
+    if (kDim > 0) {
+#pragma unroll
+        for (int d = 0; d < kDim; ++d) column_kept[d] = (kMode == kSummarise || !live) ? 0.0f : stored[(size_t)d * value_dim + j];
+    } else if (live) {
         for (int d = 0; d < head_dim; ++d) S[d * value_dim + j] = kMode == kSummarise ? 0.0f : stored[(size_t)d * value_dim + j];
+    }
 
     // rotated query and scaled rotated key of token t into buffer `b`
     auto stage = [&](int t, int b) {
@@ -91,12 +98,31 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
         float o = 0.0f;
         if (live) {
             const float vj = Num<T>::load(v + (size_t)(first + t) * in_stride + (size_t)head * value_dim + j);
-            float* column = S + j;
+            if (kDim > 0) {
+                float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // four chains of sums instead of one of kDim
+#pragma unroll
+                for (int d = 0; d < kDim; d += 4) {
+                    const float4 k4 = *reinterpret_cast<const float4*>(ks + d), q4 = *reinterpret_cast<const float4*>(qs + d);
+                    column_kept[d] = fmaf(a, column_kept[d], k4.x * vj);
+                    column_kept[d + 1] = fmaf(a, column_kept[d + 1], k4.y * vj);
+                    column_kept[d + 2] = fmaf(a, column_kept[d + 2], k4.z * vj);
+                    column_kept[d + 3] = fmaf(a, column_kept[d + 3], k4.w * vj);
+                    if (kMode != kSummarise) {
+                        part[0] = fmaf(column_kept[d], q4.x, part[0]);
+                        part[1] = fmaf(column_kept[d + 1], q4.y, part[1]);
+                        part[2] = fmaf(column_kept[d + 2], q4.z, part[2]);
+                        part[3] = fmaf(column_kept[d + 3], q4.w, part[3]);
+                    }
+                }
+                o = (part[0] + part[1]) + (part[2] + part[3]);
+            } else {
+                float* column = S + j;
 #pragma unroll 4
-            for (int d = 0; d < head_dim; ++d) {
-                const float s = fmaf(a, column[d * value_dim], ks[d] * vj);
-                column[d * value_dim] = s;
-                o = fmaf(s, qs[d], o);
+                for (int d = 0; d < head_dim; ++d) {
+                    const float s = fmaf(a, column[d * value_dim], ks[d] * vj);
+                    column[d * value_dim] = s;
+                    o = fmaf(s, qs[d], o);
+                }
             }
         }
         if (kMode == kSummarise) {
@@ -111,8 +137,14 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
         }
         __syncthreads();  // nobody still reads buffer b when the next round stages over it
     }
-    if (live && kMode != kEmit)
-        for (int d = 0; d < head_dim; ++d) stored[(size_t)d * value_dim + j] = S[d * value_dim + j];
+    if (live && kMode != kEmit) {
+        if (kDim > 0) {
+#pragma unroll
+            for (int d = 0; d < kDim; ++d) stored[(size_t)d * value_dim + j] = column_kept[d];
+        } else {
+            for (int d = 0; d < head_dim; ++d) stored[(size_t)d * value_dim + j] = S[d * value_dim + j];
+        }
+    }
 }
 
 // The runs' starting states, element by element in run order: scratch [run] holds what run `run` adds and receives the
@@ -155,20 +187,20 @@ MB_EXPORT size_t mb_retention_scratch_floats(int sequences, int heads, int head_
 
 namespace mb {
 
-template <typename T>
+template <typename T, int kDim>
 int launch_retention(const void* q, const void* k, const void* v, const void* g, int in_stride, const int* positions,
                      const float* cos_table, const float* sin_table, int rotary_dim, const float* decay, float key_scale, float eps,
                      float* state, const int* slots, const int* cu_q, int sequences, int heads, int head_dim, int value_dim, void* out,
-                     int out_stride, float out_scale, int max_q_len, int run_length, float* scratch, size_t smem, cudaStream_t stream) {
+                     int out_stride, float out_scale, int max_q_len, int run_length, float* scratch, cudaStream_t stream, size_t smem) {
     const dim3 block((value_dim + 31) / 32 * 32);
     const int runs = (run_length > 0 && max_q_len > run_length) ? (max_q_len + run_length - 1) / run_length : 1;
     if (smem > 48 * 1024) {
-        cudaFuncSetAttribute(retention_scan_kernel<T, kWhole>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cudaFuncSetAttribute(retention_scan_kernel<T, kSummarise>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cudaFuncSetAttribute(retention_scan_kernel<T, kEmit>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(retention_scan_kernel<T, kWhole, kDim>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(retention_scan_kernel<T, kSummarise, kDim>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(retention_scan_kernel<T, kEmit, kDim>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     }
 #define MB_SCAN(MODE, RUNS)                                                                                                      \
-    MB_LAUNCH("retention_scan", (retention_scan_kernel<T, MODE>), dim3(heads, sequences, RUNS), dim3(block), smem, stream, true,  \
+    MB_LAUNCH("retention_scan", (retention_scan_kernel<T, MODE, kDim>), dim3(heads, sequences, RUNS), dim3(block), smem, stream, true,  \
               (const T*)q, (const T*)k, (const T*)v, (const T*)g, in_stride, positions, cos_table, sin_table, rotary_dim, decay,  \
               key_scale, eps, state, slots, cu_q, heads, head_dim, value_dim, (T*)out, out_stride, out_scale, run_length, scratch)
     if (runs == 1) {
@@ -182,6 +214,18 @@ int launch_retention(const void* q, const void* k, const void* v, const void* g,
     MB_SCAN(kEmit, runs);
 #undef MB_SCAN
     return 0;
+}
+
+// Columns of S in registers where head_dim is one of the sizes compiled for and a block of value_dim threads may have them.
+template <typename T, typename... Args>
+int pick_retention(int head_dim, int value_dim, size_t smem_shared, size_t smem_kept, Args... args) {
+    if (value_dim <= 256) {
+        if (head_dim == 16) return launch_retention<T, 16>(args..., smem_kept);
+        if (head_dim == 32) return launch_retention<T, 32>(args..., smem_kept);
+        if (head_dim == 64) return launch_retention<T, 64>(args..., smem_kept);
+        if (head_dim == 128) return launch_retention<T, 128>(args..., smem_kept);
+    }
+    return launch_retention<T, 0>(args..., smem_shared);
 }
 
 }  // namespace mb
@@ -202,17 +246,19 @@ MB_EXPORT int mb_retention_scan(const void* q, const void* k, const void* v, con
     if (sequences > 65535) return fail("retention_scan: %d sequences exceed the grid limit 65535", sequences);
     if (run_length > 0 && max_q_len > run_length && scratch == nullptr) return fail("retention_scan: runs need scratch memory");
     if (run_length > 0 && (max_q_len + run_length - 1) / run_length > 65535) return fail("retention_scan: too many runs");
-    const size_t smem = ((size_t)head_dim * value_dim + 4 * head_dim + 32) * sizeof(float);
-    if (smem > 227 * 1024) return fail("retention_scan: a state of %d x %d floats exceeds a block's shared memory", head_dim, value_dim);
+    const size_t smem_kept = ((size_t)4 * head_dim + 32) * sizeof(float);
+    const size_t smem = smem_kept + (size_t)head_dim * value_dim * sizeof(float);
+    const bool kept = value_dim <= 256 && (head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128);
+    if (!kept && smem > 227 * 1024) return fail("retention_scan: a state of %d x %d floats exceeds a block's shared memory", head_dim, value_dim);
     int status;
     if (dtype == MB_F32)
-        status = launch_retention<float>(q, k, v, g, in_stride, positions, cos_table, sin_table, rotary_dim, decay, key_scale, eps, state,
-                                         slots, cu_q, sequences, heads, head_dim, value_dim, out, out_stride, out_scale, max_q_len,
-                                         run_length, scratch, smem, stream);
+        status = pick_retention<float>(head_dim, value_dim, smem, smem_kept, q, k, v, g, in_stride, positions, cos_table, sin_table,
+                                       rotary_dim, decay, key_scale, eps, state, slots, cu_q, sequences, heads, head_dim, value_dim, out,
+                                       out_stride, out_scale, max_q_len, run_length, scratch, stream);
     else if (dtype == MB_BF16)
-        status = launch_retention<__nv_bfloat16>(q, k, v, g, in_stride, positions, cos_table, sin_table, rotary_dim, decay, key_scale, eps,
-                                                 state, slots, cu_q, sequences, heads, head_dim, value_dim, out, out_stride, out_scale,
-                                                 max_q_len, run_length, scratch, smem, stream);
+        status = pick_retention<__nv_bfloat16>(head_dim, value_dim, smem, smem_kept, q, k, v, g, in_stride, positions, cos_table, sin_table,
+                                               rotary_dim, decay, key_scale, eps, state, slots, cu_q, sequences, heads, head_dim, value_dim,
+                                               out, out_stride, out_scale, max_q_len, run_length, scratch, stream);
     else
         return fail("retention_scan: unknown dtype code %d", dtype);
     return status ? status : check_launch("retention_scan");

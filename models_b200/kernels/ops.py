@@ -662,9 +662,12 @@ def gated_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_
         _stream()))
 
 
-def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, heads: int, gate: Optional[torch.Tensor] = None) -> None:
+def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, heads: int, gate: Optional[torch.Tensor] = None,
+                tensor_cores: bool = True) -> None:
     """One small matrix per head: out[t, h, :] = weight[h] . x[t, h, :] for weight [heads, n_out, n_in], x [T, heads * n_in],
-    out [T, heads * n_out] (column slices allowed); with `gate` [T, heads], out[t, h, :] *= sigmoid(gate[t, h])."""
+    out [T, heads * n_out] (column slices allowed); with `gate` [T, heads], out[t, h, :] *= sigmoid(gate[t, h]).
+    bfloat16 steps of 16 tokens and more with sizes that are multiples of 16 run on the tensor cores unless
+    `tensor_cores` is False."""
     _cuda(x, weight, out, gate)
     _columns(x, "x")
     _columns(out, "out")
@@ -680,7 +683,8 @@ def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, heads:
             raise KernelError(f"head_linear: gate must be [{x.shape[0]}, {heads}] of x's dtype")
     lib = gated_attention_library()
     _run(lib, lib.mb_head_linear(_p(x), x.stride(0), _p(weight), _p(out), out.stride(0), _code(x.dtype), _p(gate),
-                                 gate.stride(0) if gate is not None else 0, x.shape[0], heads, n_in, n_out, _stream()))
+                                 gate.stride(0) if gate is not None else 0, x.shape[0], heads, n_in, n_out,
+                                 1 if tensor_cores else 0, _stream()))
 
 
 RETENTION_RUN = 64  # tokens of a run when a long step's recurrence is walked in runs

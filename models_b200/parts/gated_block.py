@@ -6,7 +6,8 @@
 Both sublayers are split parts (parts/split.py): a first product, something in between, a last product.  A gate reads the
 same rows as its sublayer's first matrices, so its matrix is stacked under them and one product serves both; the last
 product's float32 result, the gate's columns of the first product and the bias then meet in one kernel that adds into the
-float32 stream.  A sublayer is thus two matrix products, its own kernels between them, and one element-wise kernel.
+float32 stream.  A sublayer is thus a norm (with few rows it rides in the first product), two matrix products, its own
+kernels between them, and one element-wise kernel.
 """
 
 from __future__ import annotations
@@ -60,22 +61,28 @@ class GatedResidualBlock(Part):
             w_in, starts = stack_rows(first)
             self.stacked.append((w_in, starts[1], rt.vector(tensors[n[bias]])))
 
-    def _sublayer(self, x, h, part, stacked, batch, run):
+    def _sublayer(self, x, norm, part, stacked, batch, run):
         w_in, gate_at, bias = stacked
         dtype = self.runtime.compute_dtype
-        proj = linear(h, w_in, dtype)
+        rows = x.shape[0]
+        if (self.runtime.mode == "bfloat16" and getattr(norm, "foldable", False) and w_in.dtype == torch.bfloat16
+                and ops.skinny_pays(w_in, rows, with_norm=True)):
+            # few rows (decode): the norm rides in the first product, which normalises the float32 rows it reads
+            proj = ops.skinny_gemm(w_in, ops.EPI_BF16, xf=x, gain=norm.weight, eps=norm.spec.eps)
+        else:
+            proj = linear(norm.forward(x, None), w_in, dtype)
         w_out = part.output_matrix()
-        mid = torch.empty((x.shape[0], w_out.shape[1]), dtype=dtype, device=x.device)
+        mid = torch.empty((rows, w_out.shape[1]), dtype=dtype, device=x.device)
         part.inner(proj[:, :part.input_matrix().shape[0]], mid, batch, run, 1.0)  # (rows of padding lie before the gate's)
         delta = linear(mid, w_out, torch.float32)
         ops.gated_residual_add(x, proj[:, gate_at:gate_at + self.width], bias, delta)
 
     def forward(self, x: torch.Tensor, pending, batch, run: RunContext):
-        h = self.mixer_norm.forward(x, as_delta(pending))
-        self._sublayer(x, h, self.mixer, self.stacked[0], batch, run)
+        if as_delta(pending) is not None:
+            ops.residual_add(x, as_delta(pending))
+        self._sublayer(x, self.mixer_norm, self.mixer, self.stacked[0], batch, run)
         if self.feed_forward is not None:
-            h = self.feed_forward_norm.forward(x, None)
-            self._sublayer(x, h, self.feed_forward, self.stacked[1], batch, run)
+            self._sublayer(x, self.feed_forward_norm, self.feed_forward, self.stacked[1], batch, run)
         return None
 
 

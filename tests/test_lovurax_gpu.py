@@ -232,7 +232,8 @@ def test_decode_runs_cover_the_page_table():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,n_in,n_out,tokens", [(1, 8, 8, 1), (3, 12, 40, 17), (5, 40, 6, 100), (4, 64, 128, 33)])
+@pytest.mark.parametrize("heads,n_in,n_out,tokens", [(1, 8, 8, 1), (3, 12, 40, 17), (5, 40, 6, 100), (4, 64, 128, 33), (2, 256, 80, 200),
+                                                     (3, 48, 256, 64)])
 def test_one_small_matrix_per_head(cuda_device, heads, n_in, n_out, tokens, dtype):
     from models_b200.kernels import ops
 
@@ -244,11 +245,13 @@ def test_one_small_matrix_per_head(cuda_device, heads, n_in, n_out, tokens, dtyp
     wide[:, 8:] = x.reshape(tokens, -1).to(dtype)
     out = torch.empty((tokens, heads * n_out), dtype=dtype, device=cuda_device)
     for g in (None, gate):
-        ops.head_linear(wide[:, 8:], w.to(dtype).to(cuda_device), out, heads, g.to(dtype).to(cuda_device) if g is not None else None)
-        want = torch.einsum("thk,hnk->thn", x, w)
-        if g is not None:
-            want = want * pl.sigmoid(g)[:, :, None]
-        assert scaled_error(out, want.reshape(tokens, -1)) < (1e-5 if dtype == torch.float32 else 1e-2)
+        for tensor_cores in (True, False):  # (the tensor-core form takes the last case's bfloat16 run)
+            ops.head_linear(wide[:, 8:], w.to(dtype).to(cuda_device), out, heads, g.to(dtype).to(cuda_device) if g is not None else None,
+                            tensor_cores)
+            want = torch.einsum("thk,hnk->thn", x, w)
+            if g is not None:
+                want = want * pl.sigmoid(g)[:, :, None]
+            assert scaled_error(out, want.reshape(tokens, -1)) < (1e-5 if dtype == torch.float32 else 1e-2), tensor_cores
 
 
 def _plain_retention(q, k, v, g, decay, rot, first_position, eps, start=None):
