@@ -354,18 +354,25 @@ def llama_like(z):
 
 
 def time_kernel(call, repeats=7):
-    """Median device time of `call()` in microseconds, L2 flushed before every run."""
+    """Median device time of `call()` in microseconds, L2 flushed before every run.  The call is replayed from a CUDA
+    graph, as the engine replays its steps: launched from Python, a kernel of a few microseconds would be timed by the
+    host's way to the launch (10 to 30 us per call), not by the device."""
     import torch
 
     flush = torch.empty(64 * 1024 * 1024, dtype=torch.float32, device="cuda")  # 256 MB > 126 MB of L2
     for _ in range(3):
         call()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        call()
+    graph.replay()
     times = []
     for _ in range(repeats):
         flush.zero_()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        call()
+        graph.replay()
         end.record()
         torch.cuda.synchronize()
         times.append(start.elapsed_time(end) * 1e3)

@@ -250,7 +250,7 @@ gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __
         if (visible) {
             const T* k_row = k_pool + (base + lane) * head_dim;
             if (vector_ok) {
-#pragma unroll 2
+#pragma unroll 4
                 for (int d = 0; d < head_dim; d += 8) {
                     float kv[8];
                     load8(k_row + d, kv);

@@ -27,11 +27,16 @@ namespace mb {
 constexpr int kWhole = 0;      // one run: from the stored state, results written, the state stored
 constexpr int kSummarise = 1;  // a run from a zero state, no results: what it adds goes to scratch [run]
 constexpr int kEmit = 2;       // a run from its starting state in scratch [run], results written
+constexpr int kTokens = 8;     // tokens of a group: their inputs are fetched together, their norms taken together
 
 // grid (heads, sequences, runs); block: value_dim rounded up to a multiple of 32 (at most 1024; 256 with kDim > 0).
 // kDim > 0: head_dim is kDim and a thread keeps its column of S in registers (a column in shared memory costs two
 // shared-memory accesses per product, which is what bounds the kernel then); kDim 0: any head_dim, columns in shared memory.
-// shared: q [2][head_dim], k [2][head_dim], 32 floats for sums, and with kDim 0 S [head_dim * value_dim].
+// A run is walked in groups of kTokens tokens: the group's rotated queries, scaled rotated keys, values and gates are
+// brought to shared memory as floats by all threads at once (one wait for memory per group instead of one per token,
+// into the buffer the group before does not use), the threads walk the group's tokens, leave their o in shared memory,
+// and the warps then take the tokens' root mean squares and write the results.
+// shared: 2 buffers [kTokens][2 head_dim + 2 value_dim], o [kTokens][value_dim], and with kDim 0 S [head_dim * value_dim].
 // scratch: [sequence][head][run][head_dim * value_dim] floats.
 template <typename T, int kMode, int kDim>
 __global__ void __launch_bounds__(kDim > 0 ? 256 : 1024)
@@ -50,9 +55,10 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
     const int first = sequence_first + run * run_length;
     const int count = kMode == kWhole ? sequence_count : min(run_length, sequence_count - run * run_length);
     if (count <= 0) return;  // the whole block leaves
-    float* qk = shared;  // [2 buffers][q | k][head_dim]
-    float* sums = qk + 4 * head_dim;
-    float* S = sums + 32;  // (kDim 0 only)
+    const int row = 2 * head_dim + 2 * value_dim;  // a token's staged floats: q, k, v, g
+    float* staged = shared;
+    float* results = staged + 2 * kTokens * row;
+    float* S = results + kTokens * value_dim;  // (kDim 0 only)
     float column_kept[kDim > 0 ? kDim : 1];
     const int j = threadIdx.x;
     const bool live = j < value_dim;
@@ -67,75 +73,99 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
         for (int d = 0; d < head_dim; ++d) S[d * value_dim + j] = kMode == kSummarise ? 0.0f : stored[(size_t)d * value_dim + j];
     }
 
-    // rotated query and scaled rotated key of token t into buffer `b`
-    auto stage = [&](int t, int b) {
-        const size_t row = (size_t)(first + t) * in_stride + (size_t)head * head_dim;
-        const int pos = positions[first + t];
-        const float* cos_row = cos_table + (size_t)pos * half;
-        const float* sin_row = sin_table + (size_t)pos * half;
-        for (int item = threadIdx.x; item < 2 * head_dim; item += blockDim.x) {
-            const bool is_key = item >= head_dim;
-            const int d = is_key ? item - head_dim : item;
-            const T* x = (is_key ? k : q) + row;
+    // the tokens t0 .. t0 + n - 1 of the run into buffer b
+    auto stage = [&](int t0, int n, int b) {
+        for (int item = threadIdx.x; item < n * row; item += blockDim.x) {
+            const int u = item / row, c = item % row;
+            const size_t token = (size_t)(first + t0 + u);
             float value;
-            if (d < half)
-                value = Num<T>::load(x + d) * cos_row[d] - Num<T>::load(x + d + half) * sin_row[d];
-            else if (d < rotary_dim)
-                value = Num<T>::load(x + d) * cos_row[d - half] + Num<T>::load(x + d - half) * sin_row[d - half];
-            else
-                value = Num<T>::load(x + d);
-            qk[b * 2 * head_dim + item] = is_key ? value * key_scale : value;
+            if (c < 2 * head_dim) {
+                const bool is_key = c >= head_dim;
+                if (kMode == kSummarise && !is_key) continue;  // no results, no queries
+                const int d = is_key ? c - head_dim : c;
+                const T* x = (is_key ? k : q) + token * in_stride + (size_t)head * head_dim;
+                if (d < rotary_dim) {
+                    const int pos = positions[token];
+                    const int pair = d < half ? d : d - half;
+                    const float cosine = cos_table[(size_t)pos * half + pair], sine = sin_table[(size_t)pos * half + pair];
+                    value = d < half ? Num<T>::load(x + d) * cosine - Num<T>::load(x + d + half) * sine
+                                     : Num<T>::load(x + d) * cosine + Num<T>::load(x + d - half) * sine;
+                } else {
+                    value = Num<T>::load(x + d);
+                }
+                if (is_key) value *= key_scale;
+            } else {
+                const bool is_gate = c >= 2 * head_dim + value_dim;
+                if (kMode == kSummarise && is_gate) continue;
+                const int d = c - 2 * head_dim - (is_gate ? value_dim : 0);
+                value = Num<T>::load((is_gate ? g : v) + token * in_stride + (size_t)head * value_dim + d);
+            }
+            staged[(b * kTokens + u) * row + c] = value;
         }
     };
 
-    stage(0, 0);
+    stage(0, min(kTokens, count), 0);
     __syncthreads();
-    for (int t = 0; t < count; ++t) {
-        const int b = t & 1;
-        if (t + 1 < count) stage(t + 1, b ^ 1);  // the next token's q and k while this one is worked on
-        const float* qs = qk + b * 2 * head_dim;
-        const float* ks = qs + head_dim;
-        float o = 0.0f;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int t0 = 0; t0 < count; t0 += kTokens) {
+        const int b = (t0 / kTokens) & 1;
+        const int n = min(kTokens, count - t0);
+        const float* group = staged + b * kTokens * row;
         if (live) {
-            const float vj = Num<T>::load(v + (size_t)(first + t) * in_stride + (size_t)head * value_dim + j);
-            if (kDim > 0) {
-                float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // four chains of sums instead of one of kDim
 #pragma unroll
-                for (int d = 0; d < kDim; d += 4) {
-                    const float4 k4 = *reinterpret_cast<const float4*>(ks + d), q4 = *reinterpret_cast<const float4*>(qs + d);
-                    column_kept[d] = fmaf(a, column_kept[d], k4.x * vj);
-                    column_kept[d + 1] = fmaf(a, column_kept[d + 1], k4.y * vj);
-                    column_kept[d + 2] = fmaf(a, column_kept[d + 2], k4.z * vj);
-                    column_kept[d + 3] = fmaf(a, column_kept[d + 3], k4.w * vj);
-                    if (kMode != kSummarise) {
-                        part[0] = fmaf(column_kept[d], q4.x, part[0]);
-                        part[1] = fmaf(column_kept[d + 1], q4.y, part[1]);
-                        part[2] = fmaf(column_kept[d + 2], q4.z, part[2]);
-                        part[3] = fmaf(column_kept[d + 3], q4.w, part[3]);
+            for (int u = 0; u < kTokens; ++u) {
+                if (u >= n) break;
+                const float* qs = group + u * row;
+                const float* ks = qs + head_dim;
+                const float vj = qs[2 * head_dim + j];
+                float o = 0.0f;
+                if (kDim > 0) {
+                    float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // four chains of sums instead of one of kDim
+#pragma unroll
+                    for (int d = 0; d < kDim; d += 4) {
+                        const float4 k4 = *reinterpret_cast<const float4*>(ks + d);
+                        column_kept[d] = fmaf(a, column_kept[d], k4.x * vj);
+                        column_kept[d + 1] = fmaf(a, column_kept[d + 1], k4.y * vj);
+                        column_kept[d + 2] = fmaf(a, column_kept[d + 2], k4.z * vj);
+                        column_kept[d + 3] = fmaf(a, column_kept[d + 3], k4.w * vj);
+                        if (kMode != kSummarise) {
+                            const float4 q4 = *reinterpret_cast<const float4*>(qs + d);
+                            part[0] = fmaf(column_kept[d], q4.x, part[0]);
+                            part[1] = fmaf(column_kept[d + 1], q4.y, part[1]);
+                            part[2] = fmaf(column_kept[d + 2], q4.z, part[2]);
+                            part[3] = fmaf(column_kept[d + 3], q4.w, part[3]);
+                        }
+                    }
+                    o = (part[0] + part[1]) + (part[2] + part[3]);
+                } else {
+                    float* column = S + j;
+#pragma unroll 4
+                    for (int d = 0; d < head_dim; ++d) {
+                        const float s = fmaf(a, column[d * value_dim], ks[d] * vj);
+                        column[d * value_dim] = s;
+                        if (kMode != kSummarise) o = fmaf(s, qs[d], o);
                     }
                 }
-                o = (part[0] + part[1]) + (part[2] + part[3]);
-            } else {
-                float* column = S + j;
-#pragma unroll 4
-                for (int d = 0; d < head_dim; ++d) {
-                    const float s = fmaf(a, column[d * value_dim], ks[d] * vj);
-                    column[d * value_dim] = s;
-                    o = fmaf(s, qs[d], o);
-                }
+                if (kMode != kSummarise) results[u * value_dim + j] = o;
             }
         }
-        if (kMode == kSummarise) {
-            __syncthreads();  // the other buffer is staged, and nobody still reads this one
-            continue;
+        if (t0 + kTokens < count) stage(t0 + kTokens, min(kTokens, count - t0 - kTokens), b ^ 1);  // the other buffer
+        __syncthreads();  // the group's o and the next group's inputs are in shared memory
+        if (kMode != kSummarise) {
+            for (int u = warp; u < n; u += warps) {  // a warp per token: root mean square of the head's o, gate, store
+                const float* o_row = results + u * value_dim;
+                const float* gate_row = group + u * row + 2 * head_dim + value_dim;
+                float ssq = 0.0f;
+                for (int d = lane; d < value_dim; d += 32) ssq = fmaf(o_row[d], o_row[d], ssq);
+                const float inverse = out_scale / sqrtf(warp_sum(ssq) / (float)value_dim + eps);
+                T* out_row = out + (size_t)(first + t0 + u) * out_stride + (size_t)head * value_dim;
+                for (int d = lane; d < value_dim; d += 32) {
+                    const float gate = gate_row[d];
+                    Num<T>::store(out_row + d, o_row[d] * inverse * (gate / (1.0f + expf(-gate))));
+                }
+            }
+            __syncthreads();  // the next group writes its o over these
         }
-        const float ssq = block_sum(o * o, sums);  // (two barriers inside: the other buffer is staged when it returns)
-        if (live) {
-            const float gate = Num<T>::load(g + (size_t)(first + t) * in_stride + (size_t)head * value_dim + j);
-            const float y = o / sqrtf(ssq / (float)value_dim + eps) * (gate / (1.0f + expf(-gate)));
-            Num<T>::store(out + (size_t)(first + t) * out_stride + (size_t)head * value_dim + j, out_scale * y);
-        }
-        __syncthreads();  // nobody still reads buffer b when the next round stages over it
     }
     if (live && kMode != kEmit) {
         if (kDim > 0) {
@@ -219,7 +249,7 @@ int launch_retention(const void* q, const void* k, const void* v, const void* g,
 // Columns of S in registers where head_dim is one of the sizes compiled for and a block of value_dim threads may have them.
 template <typename T, typename... Args>
 int pick_retention(int head_dim, int value_dim, size_t smem_shared, size_t smem_kept, Args... args) {
-    if (value_dim <= 256) {
+    if (value_dim <= 256 && value_dim % 2 == 0) {  // (even: a token's staged floats then start on 16 bytes)
         if (head_dim == 16) return launch_retention<T, 16>(args..., smem_kept);
         if (head_dim == 32) return launch_retention<T, 32>(args..., smem_kept);
         if (head_dim == 64) return launch_retention<T, 64>(args..., smem_kept);
@@ -246,9 +276,9 @@ MB_EXPORT int mb_retention_scan(const void* q, const void* k, const void* v, con
     if (sequences > 65535) return fail("retention_scan: %d sequences exceed the grid limit 65535", sequences);
     if (run_length > 0 && max_q_len > run_length && scratch == nullptr) return fail("retention_scan: runs need scratch memory");
     if (run_length > 0 && (max_q_len + run_length - 1) / run_length > 65535) return fail("retention_scan: too many runs");
-    const size_t smem_kept = ((size_t)4 * head_dim + 32) * sizeof(float);
+    const size_t smem_kept = ((size_t)2 * kTokens * (2 * head_dim + 2 * value_dim) + (size_t)kTokens * value_dim) * sizeof(float);
     const size_t smem = smem_kept + (size_t)head_dim * value_dim * sizeof(float);
-    const bool kept = value_dim <= 256 && (head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128);
+    const bool kept = value_dim <= 256 && value_dim % 2 == 0 && (head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128);
     if (!kept && smem > 227 * 1024) return fail("retention_scan: a state of %d x %d floats exceeds a block's shared memory", head_dim, value_dim);
     int status;
     if (dtype == MB_F32)
