@@ -182,6 +182,25 @@ gated_attention_rows_kernel(const T* __restrict__ q, int q_stride, T* __restrict
     }
 }
 
+// kVec consecutive elements (4 or 8) as floats; the address is a multiple of kVec elements.
+template <int kVec>
+__device__ __forceinline__ void load_vec(const float* p, float* v) {
+#pragma unroll
+    for (int i = 0; i < kVec; i += 4) {
+        const float4 a = *reinterpret_cast<const float4*>(p + i);
+        v[i] = a.x, v[i + 1] = a.y, v[i + 2] = a.z, v[i + 3] = a.w;
+    }
+}
+template <int kVec>
+__device__ __forceinline__ void load_vec(const __nv_bfloat16* p, float* v) {
+#pragma unroll
+    for (int i = 0; i < kVec; i += 4) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p + i);
+        v[i] = __uint_as_float(raw.x << 16), v[i + 1] = __uint_as_float(raw.x & 0xffff0000u);
+        v[i + 2] = __uint_as_float(raw.y << 16), v[i + 3] = __uint_as_float(raw.y & 0xffff0000u);
+    }
+}
+
 // ------------------------------------------------------------------------------------------------
 // Decoding: one query token per sequence.  A warp per (sequence, head) cannot keep a GPU busy with a handful of
 // sequences, and it reads a key/value head once per query head that shares it.  Here the keys of a sequence are cut
@@ -228,6 +247,8 @@ gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __
     for (int i = threadIdx.x; i < count * head_dim; i += blockDim.x) q_shared[i] = Num<T>::load(q_row + i);
     __syncthreads();
     const bool vector_ok = (head_dim % 8) == 0 && (((size_t)k_pool) & (sizeof(T) * 8 - 1)) == 0;
+    constexpr int kVec = kAcc >= 8 ? 8 : 4;  // neighbouring value coordinates a lane holds
+    const bool values_vector_ok = (v_width % kVec) == 0 && (((size_t)v_pool) & (sizeof(T) * kVec - 1)) == 0;
     float slope[kGroup], bias[kGroup], run_max[kGroup], run_sum[kGroup], acc[kGroup][kAcc];
 #pragma unroll
     for (int g = 0; g < kGroup; ++g) {
@@ -250,7 +271,7 @@ gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __
         if (visible) {
             const T* k_row = k_pool + (base + lane) * head_dim;
             if (vector_ok) {
-#pragma unroll 4
+#pragma unroll 8
                 for (int d = 0; d < head_dim; d += 8) {
                     float kv[8];
                     load8(k_row + d, kv);
@@ -291,7 +312,7 @@ gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __
             }
         }
         // the values of kAhead keys are asked for before the first is used (a key beyond the run's end has weight 0 and
-        // reads the run's last row again)
+        // reads the run's last row again); a lane holds kVec neighbouring coordinates of every 32 * kVec, one load each
         constexpr int kAhead = kAcc <= 4 ? 8 : 4;
         const int last = min(31, end - 1 - chunk);
         for (int j0 = 0; j0 <= last; j0 += kAhead) {
@@ -300,7 +321,15 @@ gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __
             for (int u = 0; u < kAhead; ++u) {
                 const T* v_row = v_pool + (base + min(j0 + u, last)) * v_width;
 #pragma unroll
-                for (int i = 0; i < kAcc; ++i) value[u][i] = lane + 32 * i < value_dim ? Num<T>::load(v_row + lane + 32 * i) : 0.0f;
+                for (int part = 0; part < kAcc / kVec; ++part) {
+                    const int d = part * 32 * kVec + lane * kVec;
+                    if (values_vector_ok && d + kVec <= value_dim) {
+                        load_vec<kVec>(v_row + d, &value[u][part * kVec]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < kVec; ++i) value[u][part * kVec + i] = d + i < value_dim ? Num<T>::load(v_row + d + i) : 0.0f;
+                    }
+                }
             }
 #pragma unroll
             for (int u = 0; u < kAhead; ++u) {
@@ -323,8 +352,10 @@ gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __
                 mine[1] = run_sum[g];
             }
 #pragma unroll
-            for (int i = 0; i < kAcc; ++i)
-                if (lane + 32 * i < value_dim) mine[2 + lane + 32 * i] = acc[g][i];
+            for (int i = 0; i < kAcc; ++i) {
+                const int d = (i / kVec) * 32 * kVec + lane * kVec + i % kVec;
+                if (d < value_dim) mine[2 + d] = acc[g][i];
+            }
         }
     }
     __syncthreads();
@@ -380,11 +411,12 @@ __global__ void gated_attention_combine_kernel(const float* __restrict__ partial
 
 // out[t, h * n_out + n] = gate * sum_k in[t, h * n_in + k] * w[(h * n_out + n) * n_in + k]: one small matrix per head,
 // rows of n_in weights; gate: sigmoid of gate[t, h] when given.
-// Plain arithmetic: grid (ceil(tokens / 16), heads, ceil(n_out / 32)); block 128.  A warp takes 8 of the block's 32
-// outputs in turn: its lanes walk a weight row together (neighbouring lanes read neighbouring weights), each with a sum
-// per token, and the sums meet by shuffles.  shared: 16 * n_in floats.
+// Plain arithmetic: grid (ceil(tokens / 16), heads, ceil(n_out / 8)); block 128.  A warp takes 2 of the block's 8
+// outputs in turn (few, so that a decode step's handful of tokens still spreads over the multiprocessors and no warp
+// waits for memory many times in a row): its lanes walk a weight row together (neighbouring lanes read neighbouring
+// weights), each with a sum per token, and the sums meet by shuffles.  shared: 16 * n_in floats.
 constexpr int kHeadRows = 16;
-constexpr int kHeadOutputs = 32;
+constexpr int kHeadOutputs = 8;
 
 template <typename T>
 __global__ void head_linear_kernel(const T* __restrict__ in, int in_stride, const T* __restrict__ w, T* __restrict__ out,
@@ -407,10 +439,16 @@ __global__ void head_linear_kernel(const T* __restrict__ in, int in_stride, cons
         float acc[kHeadRows];
 #pragma unroll
         for (int r = 0; r < kHeadRows; ++r) acc[r] = 0.0f;
-        for (int k = lane; k < n_in; k += 32) {
-            const float weight = Num<T>::load(w_row + k);
+        for (int k0 = lane; k0 < n_in; k0 += 32 * 8) {  // eight of the row's weights are asked for before the first is used
+            float weight[8];
 #pragma unroll
-            for (int r = 0; r < kHeadRows; ++r) acc[r] = fmaf(rows_shared[r * n_in + k], weight, acc[r]);
+            for (int u = 0; u < 8; ++u) weight[u] = k0 + 32 * u < n_in ? Num<T>::load(w_row + k0 + 32 * u) : 0.0f;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int k = min(k0 + 32 * u, n_in - 1);  // (beyond the row the weight is 0)
+#pragma unroll
+                for (int r = 0; r < kHeadRows; ++r) acc[r] = fmaf(rows_shared[r * n_in + k], weight[u], acc[r]);
+            }
         }
         // lane r ends up with token r's sum (every sum is added over the lanes in the same order)
         float mine = 0.0f;

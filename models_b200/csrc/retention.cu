@@ -73,34 +73,41 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
         for (int d = 0; d < head_dim; ++d) S[d * value_dim + j] = kMode == kSummarise ? 0.0f : stored[(size_t)d * value_dim + j];
     }
 
-    // the tokens t0 .. t0 + n - 1 of the run into buffer b
+    // The tokens t0 .. t0 + n - 1 of the run into buffer b.  A thread takes coordinate c of the staged row [q | k | v | g]
+    // for all tokens of the group: what c is (which tensor, rotated or not, its pair) is worked out once, and the
+    // group's loads are all asked for before the first is stored.  A sequence's new tokens stand at consecutive
+    // positions, so a token's position follows from the first one's without a load per token.
+    const int position0 = positions[sequence_first] + run * run_length;
     auto stage = [&](int t0, int n, int b) {
-        for (int item = threadIdx.x; item < n * row; item += blockDim.x) {
-            const int u = item / row, c = item % row;
-            const size_t token = (size_t)(first + t0 + u);
-            float value;
-            if (c < 2 * head_dim) {
-                const bool is_key = c >= head_dim;
-                if (kMode == kSummarise && !is_key) continue;  // no results, no queries
-                const int d = is_key ? c - head_dim : c;
-                const T* x = (is_key ? k : q) + token * in_stride + (size_t)head * head_dim;
-                if (d < rotary_dim) {
-                    const int pos = positions[token];
-                    const int pair = d < half ? d : d - half;
-                    const float cosine = cos_table[(size_t)pos * half + pair], sine = sin_table[(size_t)pos * half + pair];
-                    value = d < half ? Num<T>::load(x + d) * cosine - Num<T>::load(x + d + half) * sine
-                                     : Num<T>::load(x + d) * cosine + Num<T>::load(x + d - half) * sine;
-                } else {
-                    value = Num<T>::load(x + d);
+        for (int c = threadIdx.x; c < row; c += blockDim.x) {
+            const bool is_qk = c < 2 * head_dim;
+            const bool is_key = is_qk && c >= head_dim;
+            const bool is_gate = !is_qk && c >= 2 * head_dim + value_dim;
+            if (kMode == kSummarise && ((is_qk && !is_key) || is_gate)) continue;  // no results: no queries, no gates
+            const int d = is_qk ? (is_key ? c - head_dim : c) : c - 2 * head_dim - (is_gate ? value_dim : 0);
+            const T* source = (is_qk ? (is_key ? k : q) + (size_t)head * head_dim : (is_gate ? g : v) + (size_t)head * value_dim)
+                              + (size_t)(first + t0) * in_stride;
+            const bool rotated = is_qk && d < rotary_dim;
+            const int pair = d < half ? d : d - half;
+            const int other = d < half ? d + half : d - half;
+            const float sign = d < half ? -1.0f : 1.0f;
+            float value[kTokens];
+#pragma unroll
+            for (int u = 0; u < kTokens; ++u) {
+                value[u] = 0.0f;
+                if (u < n) {
+                    const T* x = source + (size_t)u * in_stride;
+                    value[u] = Num<T>::load(x + d);
+                    if (rotated) {
+                        const size_t at = (size_t)(position0 + t0 + u) * half + pair;
+                        value[u] = value[u] * cos_table[at] + sign * Num<T>::load(x + other) * sin_table[at];
+                    }
                 }
-                if (is_key) value *= key_scale;
-            } else {
-                const bool is_gate = c >= 2 * head_dim + value_dim;
-                if (kMode == kSummarise && is_gate) continue;
-                const int d = c - 2 * head_dim - (is_gate ? value_dim : 0);
-                value = Num<T>::load((is_gate ? g : v) + token * in_stride + (size_t)head * value_dim + d);
             }
-            staged[(b * kTokens + u) * row + c] = value;
+            const float factor = is_key ? key_scale : 1.0f;
+#pragma unroll
+            for (int u = 0; u < kTokens; ++u)
+                if (u < n) staged[(b * kTokens + u) * row + c] = value[u] * factor;
         }
     };
 
@@ -194,11 +201,20 @@ __global__ void retention_prefix_kernel(float* __restrict__ scratch, float* __re
     const float a = decay[head];
     const float whole_run = powf(a, (float)run_length);
     float s = *stored;
-    for (int run = 0; run * run_length < count; ++run) {
-        const int n = min(run_length, count - run * run_length);
-        const float added = mine[(size_t)run * elements];
-        mine[(size_t)run * elements] = s;
-        s = fmaf(n == run_length ? whole_run : powf(a, (float)n), s, added);
+    const int used = (count + run_length - 1) / run_length;
+    for (int run0 = 0; run0 < used; run0 += 8) {  // eight runs' additions are asked for before the first start is stored
+        float added[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) added[u] = run0 + u < used ? mine[(size_t)(run0 + u) * elements] : 0.0f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int run = run0 + u;
+            if (run < used) {
+                const int n = min(run_length, count - run * run_length);
+                mine[(size_t)run * elements] = s;
+                s = fmaf(n == run_length ? whole_run : powf(a, (float)n), s, added[u]);
+            }
+        }
     }
     *stored = s;
 }

@@ -573,12 +573,15 @@ def gated_attention_tc_takes(q: torch.Tensor, out: torch.Tensor, k_pool: torch.T
 
 
 def gated_decode_runs(sequences: int, heads: int, kv_heads: int, pages: int, multiprocessors: int = 148):
-    """(runs, pages per run) for a decode step whose page tables are `pages` wide: as many runs as give every
-    multiprocessor two blocks, at most one per page and at most 64."""
+    """(runs, pages per run) for a decode step whose page tables are `pages` wide.  A block's four warps take a run's
+    chunks of 32 keys in turn, and a warp's chunks cost it one wait for memory after another: runs of two pages (a chunk
+    per warp) as long as that makes at most 64 runs and no more than eight blocks per multiprocessor, longer ones beyond."""
     group = heads // kv_heads
     blocks = sequences * kv_heads * (-(-group // (4 if group <= 4 else 8)))
-    wanted = max(1, min(64, pages, -(-2 * multiprocessors // blocks)))
-    span = -(-pages // wanted)
+    span = max(2 if pages > 1 else 1, -(-pages // 64))
+    while span < pages and blocks * (-(-pages // span)) > 8 * multiprocessors:
+        span *= 2
+    span = min(span, pages)
     return -(-pages // span), span
 
 
@@ -703,6 +706,7 @@ def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.T
     (split-half pairs, float32 tables by position), k times key_scale; S = decay_h S + k v^T from the sequence's row of
     `state` (float32 [slots, heads, head_dim, value_dim], updated in place); o = S^T q; out = out_scale * o / rms(o) *
     silu(g) per head, rms(o) = sqrt(mean(o^2) + eps).  q, k, v, g are column slices with one row stride.
+    Of `positions` only each sequence's first entry is read: its new tokens stand at consecutive positions.
     `max_q_len`: the most new tokens of any sequence.  Beyond `run_length` tokens (None: RETENTION_RUN once a step brings
     more than twice as many) the sequences are walked in runs of that many tokens at once, through scratch memory."""
     _cuda(q, k, v, g, positions, cos, sin, decay, state, slots, cu_q, out)
