@@ -182,25 +182,6 @@ gated_attention_rows_kernel(const T* __restrict__ q, int q_stride, T* __restrict
     }
 }
 
-// kVec consecutive elements (4 or 8) as floats; the address is a multiple of kVec elements.
-template <int kVec>
-__device__ __forceinline__ void load_vec(const float* p, float* v) {
-#pragma unroll
-    for (int i = 0; i < kVec; i += 4) {
-        const float4 a = *reinterpret_cast<const float4*>(p + i);
-        v[i] = a.x, v[i + 1] = a.y, v[i + 2] = a.z, v[i + 3] = a.w;
-    }
-}
-template <int kVec>
-__device__ __forceinline__ void load_vec(const __nv_bfloat16* p, float* v) {
-#pragma unroll
-    for (int i = 0; i < kVec; i += 4) {
-        const uint2 raw = *reinterpret_cast<const uint2*>(p + i);
-        v[i] = __uint_as_float(raw.x << 16), v[i + 1] = __uint_as_float(raw.x & 0xffff0000u);
-        v[i + 2] = __uint_as_float(raw.y << 16), v[i + 3] = __uint_as_float(raw.y & 0xffff0000u);
-    }
-}
-
 // ------------------------------------------------------------------------------------------------
 // Decoding: one query token per sequence.  A warp per (sequence, head) cannot keep a GPU busy with a handful of
 // sequences, and it reads a key/value head once per query head that shares it.  Here the keys of a sequence are cut
@@ -247,8 +228,6 @@ gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __
     for (int i = threadIdx.x; i < count * head_dim; i += blockDim.x) q_shared[i] = Num<T>::load(q_row + i);
     __syncthreads();
     const bool vector_ok = (head_dim % 8) == 0 && (((size_t)k_pool) & (sizeof(T) * 8 - 1)) == 0;
-    constexpr int kVec = kAcc >= 8 ? 8 : 4;  // neighbouring value coordinates a lane holds
-    const bool values_vector_ok = (v_width % kVec) == 0 && (((size_t)v_pool) & (sizeof(T) * kVec - 1)) == 0;
     float slope[kGroup], bias[kGroup], run_max[kGroup], run_sum[kGroup], acc[kGroup][kAcc];
 #pragma unroll
     for (int g = 0; g < kGroup; ++g) {
@@ -312,7 +291,7 @@ gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __
             }
         }
         // the values of kAhead keys are asked for before the first is used (a key beyond the run's end has weight 0 and
-        // reads the run's last row again); a lane holds kVec neighbouring coordinates of every 32 * kVec, one load each
+        // reads the run's last row again)
         constexpr int kAhead = kAcc <= 4 ? 8 : 4;
         const int last = min(31, end - 1 - chunk);
         for (int j0 = 0; j0 <= last; j0 += kAhead) {
@@ -321,15 +300,7 @@ gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __
             for (int u = 0; u < kAhead; ++u) {
                 const T* v_row = v_pool + (base + min(j0 + u, last)) * v_width;
 #pragma unroll
-                for (int part = 0; part < kAcc / kVec; ++part) {
-                    const int d = part * 32 * kVec + lane * kVec;
-                    if (values_vector_ok && d + kVec <= value_dim) {
-                        load_vec<kVec>(v_row + d, &value[u][part * kVec]);
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < kVec; ++i) value[u][part * kVec + i] = d + i < value_dim ? Num<T>::load(v_row + d + i) : 0.0f;
-                    }
-                }
+                for (int i = 0; i < kAcc; ++i) value[u][i] = lane + 32 * i < value_dim ? Num<T>::load(v_row + lane + 32 * i) : 0.0f;
             }
 #pragma unroll
             for (int u = 0; u < kAhead; ++u) {
@@ -352,10 +323,8 @@ gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __
                 mine[1] = run_sum[g];
             }
 #pragma unroll
-            for (int i = 0; i < kAcc; ++i) {
-                const int d = (i / kVec) * 32 * kVec + lane * kVec + i % kVec;
-                if (d < value_dim) mine[2 + d] = acc[g][i];
-            }
+            for (int i = 0; i < kAcc; ++i)
+                if (lane + 32 * i < value_dim) mine[2 + lane + 32 * i] = acc[g][i];
         }
     }
     __syncthreads();
