@@ -469,7 +469,7 @@ LOVURAX_ORDER = ("attention", "retention", "attention", "latent_attention")
 def lovurax_config(z):
     H, D, DV = z["heads"], z["dim"], z["vdim"]
     mixers = {
-        "attention": {"heads": H, "kv_heads": z["kv_heads"], "dim": D, "vdim": DV, "scale": D ** -0.5, "q_temp": {"coef": 0.5, "every": 256}},
+        "attention": {"heads": H, "kv_heads": z["kv_heads"], "dim": D, "vdim": DV, "scale": D ** -0.5, "q_temp": {"coef": 0.4, "every": 128}},
         "retention": {"heads": H, "dim": D, "vdim": DV, "decay": [1.0 - 2.0 ** (-5 - 3 * h / max(1, H - 1)) for h in range(H)],
                       "rot": {"dims": D // 2, "base": 500000.0}},
         "latent_attention": {"heads": H, "dim": D, "vdim": DV, "kv_rank": z["rank"], "scale": D ** -0.5},

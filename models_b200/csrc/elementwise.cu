@@ -443,6 +443,26 @@ __global__ void gated_residual_add_kernel(float* __restrict__ x, const TG* __res
     }
 }
 
+// Eight elements a thread (width and the gate's stride are multiples of 8, every row starts on 16 bytes; 32 for floats).
+template <typename TG, typename TD>
+__global__ void gated_residual_add_vec8_kernel(float* __restrict__ x, const TG* __restrict__ gate, int gate_stride,
+                                               const float* __restrict__ bias, const TD* __restrict__ delta, int width8,
+                                               size_t total8) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / width8, c = (i % width8) * 8;
+        float z[8], b[8], d[8], v[8];
+        load8(gate + r * gate_stride + c, z);
+        load8(bias + c, b);
+        load8(delta + i * 8, d);
+        load8(x + i * 8, v);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = fmaf(1.0f / (1.0f + expf(-(z[k] + b[k]))), d[k], v[k]);
+        store8(x + i * 8, v);
+    }
+}
+
 }  // namespace mb
 
 using namespace mb;
@@ -700,21 +720,35 @@ MB_EXPORT int mb_xielu(const void* src, int src_stride, void* dst, int dst_strid
 }
 
 // x += sigmoid(gate + bias) * delta; gate and delta each float or bfloat16.
+namespace mb {
+template <typename TG, typename TD>
+int launch_gated_residual_add(float* x, const void* gate, int gate_stride, const float* bias, const void* delta, int rows,
+                              int width, cudaStream_t stream) {
+    const size_t total = (size_t)rows * width;
+    const size_t gate_align = sizeof(TG) * 8 - 1, delta_align = sizeof(TD) * 8 - 1;
+    if (width % 8 == 0 && gate_stride % 8 == 0 && !((uintptr_t)x & 31) && !((uintptr_t)bias & 31) && !((uintptr_t)gate & gate_align) &&
+        !((uintptr_t)delta & delta_align)) {
+        MB_LAUNCH("elementwise", (gated_residual_add_vec8_kernel<TG, TD>), dim3(grid_for(total / 8, 256)), dim3(256), 0, stream, true, x,
+                  (const TG*)gate, gate_stride, bias, (const TD*)delta, width / 8, total / 8);
+    } else {
+        MB_LAUNCH("elementwise", (gated_residual_add_kernel<TG, TD>), dim3(grid_for(total, 256)), dim3(256), 0, stream, true, x,
+                  (const TG*)gate, gate_stride, bias, (const TD*)delta, width, total);
+    }
+    return 0;
+}
+}  // namespace mb
+
 MB_EXPORT int mb_gated_residual_add(float* x, const void* gate, int gate_stride, int gate_dtype, const float* bias,
                                     const void* delta, int delta_dtype, int rows, int width, cudaStream_t stream) {
     if (rows <= 0 || width <= 0) return 0;
-    const size_t total = (size_t)rows * width;
-    const dim3 grid(grid_for(total, 256)), block(256);
+    int status;
     if (gate_dtype == MB_F32 && delta_dtype == MB_F32)
-        MB_LAUNCH("elementwise", gated_residual_add_kernel<float, float>, dim3(grid), dim3(block), 0, stream, true, x,
-                  (const float*)gate, gate_stride, bias, (const float*)delta, width, total);
+        status = mb::launch_gated_residual_add<float, float>(x, gate, gate_stride, bias, delta, rows, width, stream);
     else if (gate_dtype == MB_BF16 && delta_dtype == MB_F32)
-        MB_LAUNCH("elementwise", gated_residual_add_kernel<__nv_bfloat16, float>, dim3(grid), dim3(block), 0, stream, true, x,
-                  (const __nv_bfloat16*)gate, gate_stride, bias, (const float*)delta, width, total);
+        status = mb::launch_gated_residual_add<__nv_bfloat16, float>(x, gate, gate_stride, bias, delta, rows, width, stream);
     else if (gate_dtype == MB_BF16 && delta_dtype == MB_BF16)
-        MB_LAUNCH("elementwise", gated_residual_add_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(block), 0, stream, true,
-                  x, (const __nv_bfloat16*)gate, gate_stride, bias, (const __nv_bfloat16*)delta, width, total);
+        status = mb::launch_gated_residual_add<__nv_bfloat16, __nv_bfloat16>(x, gate, gate_stride, bias, delta, rows, width, stream);
     else
         return fail("gated_residual_add: gate dtype %d with delta dtype %d is not built", gate_dtype, delta_dtype);
-    return check_launch("gated_residual_add");
+    return status ? status : check_launch("gated_residual_add");
 }

@@ -539,7 +539,9 @@ int launch_norm_store(void* q, int q_stride, const void* k, int k_stride, const 
                       const float* q_gain, const float* k_gain, float eps, float temp_coef, int temp_every, void* k_pool,
                       void* v_pool, const int* slot_mapping, int tokens, int heads, int kv_heads, int head_dim, int value_dim,
                       int page_size, cudaStream_t stream) {
-    MB_LAUNCH("norm_store", norm_store_kernel<T>, dim3(tokens), dim3(128), 0, stream, true, (T*)q, q_stride, (const T*)k,
+    // a warp per head where a block can have that many (up to 16): a head costs its warp two waits for memory
+    const int warps = heads + kv_heads < 4 ? 4 : (heads + kv_heads > 16 ? 16 : heads + kv_heads);
+    MB_LAUNCH("norm_store", norm_store_kernel<T>, dim3(tokens), dim3(32 * warps), 0, stream, true, (T*)q, q_stride, (const T*)k,
               k_stride, (const T*)v, v_stride, positions, q_gain, k_gain, eps, temp_coef, temp_every, (T*)k_pool, (T*)v_pool,
               slot_mapping, heads, kv_heads, head_dim, value_dim, page_size);
     return 0;

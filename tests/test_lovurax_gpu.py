@@ -272,7 +272,7 @@ def _plain_retention(q, k, v, g, decay, rot, first_position, eps, start=None):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("run_length", [0, 16, 7])
 @pytest.mark.parametrize("heads,dim,vdim,rot,decay", [(2, 16, 24, (8, 10000.0), [0.9, 0.999]), (1, 32, 32, (32, 50.0), [1.0]),
-                                                      (3, 10, 6, (0, 1.0), [0.5, 0.0, 0.97]), (2, 64, 128, (32, 1e6), [0.99, 0.95]),
+                                                      (3, 10, 6, (0, 1.0), [0.5, 0.0, 0.97]), (2, 64, 128, (48, 2e5), [0.99, 0.95]),
                                                       (2, 32, 7, (16, 300.0), [0.9, 0.8]), (1, 128, 256, (64, 1e4), [0.98])])
 def test_retention_ragged_carried_and_rotated(cuda_device, heads, dim, vdim, rot, decay, run_length, dtype):
     """Sequences of unequal lengths in one call, then one more token for each (the state is carried in float32 between

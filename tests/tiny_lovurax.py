@@ -53,7 +53,7 @@ LVX_B = {
 # sizes at which the tensor-core products run (multiples of 64 and more than 128 rows in a prompt)
 LVX_C = {
     "architecture": "Lovurax", "vocab": 512, "width": 256, "norm": {"eps": 1e-5}, "logit_scale": 0.5,
-    "layers": [attention(8, 2, 64, 64, 0.125, (0.5, 64), 512),
+    "layers": [attention(8, 2, 64, 64, 0.125, (0.4, 64), 512),
                latent(4, 64, 64, 128, 0.125, 256),
                retention(4, 64, 128, [0.97, 0.99, 0.999, 0.9], (32, 100000.0), 512)],
 }
