@@ -106,6 +106,10 @@ struct SkinnyArgs {
     bf16* emit_rows;          // [batch][ld_emit]
     int ld_emit;
     float* emit_ssq;
+    // EPI_RESIDUAL, optional: what is added is first multiplied by sigmoid(gate[b][row] + gate_bias[row]) (a gated residual)
+    const bf16* gate;         // [batch][ld_gate]
+    int ld_gate;
+    const float* gate_bias;   // [n]
     const int* rows;      // optional: activation row b is xf row rows[b]
     bf16* out_bf16;
     float* out_f32;       // EPI_F32 output, or the residual stream for EPI_RESIDUAL
@@ -440,6 +444,10 @@ skinny_gemm_kernel(const SkinnyArgs args) {
             if (EPI == EPI_BF16) args.out_bf16[at] = __float2bfloat16_rn(value);
             if (EPI == EPI_F32) args.out_f32[at] = value;
             if (EPI == EPI_RESIDUAL) {
+                if (args.gate != nullptr) {
+                    const float z = __bfloat162float(args.gate[(size_t)col * args.ld_gate + row]) + args.gate_bias[row];
+                    value *= 1.0f / (1.0f + expf(-z));
+                }
                 const float x_new = (i == (int)threadIdx.x ? early_a : args.out_f32[at]) + value;
                 args.out_f32[at] = x_new;
                 if (emits) {
@@ -635,6 +643,18 @@ MB_EXPORT int mb_skinny_gemm(const void* w, int ldw, int n, int k, int batch, co
     if (parts_written) *parts_written = (n + 15) / 16;
     return skinny_gemm(w, ldw, n, k, batch, x, ldx, xf, ldxf, gain, eps, rows, out, ld_out, epilogue, multiprocessors, dependent,
                        args, stream);
+}
+
+// x_out += sigmoid(gate + gate_bias) * (x . w^T): the residual epilogue with a gate on what is added.  gate: bfloat16
+// [batch, n] rows (row stride ld_gate), gate_bias: float [n].
+MB_EXPORT int mb_skinny_gemm_gated_residual(const void* w, int ldw, int n, int k, int batch, const void* x, int ldx, void* out,
+                                            int ld_out, const void* gate, int ld_gate, const float* gate_bias, int multiprocessors,
+                                            int dependent, cudaStream_t stream) {
+    if (!gate || !gate_bias) return fail("skinny_gemm_gated_residual: needs the gate's rows and its bias");
+    SkinnyArgs args{};
+    args.gate = (const bf16*)gate; args.ld_gate = ld_gate; args.gate_bias = gate_bias;
+    return skinny_gemm(w, ldw, n, k, batch, x, ldx, nullptr, 0, nullptr, 0.0f, nullptr, out, ld_out, EPI_RESIDUAL, multiprocessors,
+                       dependent, args, stream);
 }
 
 // The q/k/v product of an attention layer with rotation and cache write folded in.  w: [(heads + 2 *

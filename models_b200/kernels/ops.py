@@ -1039,6 +1039,26 @@ def skinny_gemm(weight: torch.Tensor, epilogue: int, x: Optional[torch.Tensor] =
     return out
 
 
+def skinny_gemm_gated_residual(weight: torch.Tensor, x: torch.Tensor, out: torch.Tensor, gate: torch.Tensor, bias: torch.Tensor) -> None:
+    """out += sigmoid(gate + bias) * (x . weight^T) for few rows: the residual epilogue of the decode product with a
+    gate on what it adds.  x bfloat16 [rows, k], weight bfloat16 [n, k], out the float32 stream [rows, n], gate bfloat16
+    [rows, n] (a column slice is fine), bias float32 [n]."""
+    _cuda(weight, x, out, gate, bias)
+    n, k = weight.shape
+    batch = x.shape[0]
+    if x.dtype != torch.bfloat16 or x.stride(1) != 1 or x.shape[1] != k or not skinny_takes(weight, batch):
+        raise KernelError(f"skinny_gemm_gated_residual does not take a {tuple(weight.shape)} weight with {tuple(x.shape)} {x.dtype} rows")
+    if out.dtype != torch.float32 or tuple(out.shape) != (batch, n) or out.stride(1) != 1:
+        raise KernelError("the residual epilogue adds into a float32 [rows, n] tensor")
+    _columns(gate, "gate")
+    if gate.dtype != torch.bfloat16 or tuple(gate.shape) != (batch, n) or bias.dtype != torch.float32 or bias.numel() != n \
+            or not bias.is_contiguous():
+        raise KernelError("the gate must be bfloat16 [rows, n] and its bias float32 [n]")
+    lib = skinny()
+    _run(lib, lib.mb_skinny_gemm_gated_residual(_p(weight), weight.stride(0), n, k, batch, _p(x), x.stride(0), _p(out), out.stride(0),
+                                                _p(gate), gate.stride(0), _p(bias), _sm_count(weight.device), 1, _stream()))
+
+
 def skinny_qkv_rope(weight: torch.Tensor, xf: Optional[torch.Tensor], gain: Optional[torch.Tensor], eps: float, heads: int,
                     kv_heads: int, head_dim: int, positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
                     k_pool: torch.Tensor, v_pool: torch.Tensor, slot_mapping: torch.Tensor, x: Optional[torch.Tensor] = None,

@@ -6,8 +6,9 @@
 Both sublayers are split parts (parts/split.py): a first product, something in between, a last product.  A gate reads the
 same rows as its sublayer's first matrices, so its matrix is stacked under them and one product serves both; the last
 product's float32 result, the gate's columns of the first product and the bias then meet in one kernel that adds into the
-float32 stream.  A sublayer is thus a norm (with few rows it rides in the first product), two matrix products, its own
-kernels between them, and one element-wise kernel.
+float32 stream.  A sublayer is thus a norm, two matrix products, its own
+kernels between them, and one element-wise kernel; with few rows (decode) the norm rides in the first product and the
+gated add in the last one's epilogue.
 """
 
 from __future__ import annotations
@@ -74,8 +75,13 @@ class GatedResidualBlock(Part):
         w_out = part.output_matrix()
         mid = torch.empty((rows, w_out.shape[1]), dtype=dtype, device=x.device)
         part.inner(proj[:, :part.input_matrix().shape[0]], mid, batch, run, 1.0)  # (rows of padding lie before the gate's)
+        gate = proj[:, gate_at:gate_at + self.width]
+        if (self.runtime.mode == "bfloat16" and w_out.dtype == torch.bfloat16 and proj.dtype == torch.bfloat16
+                and ops.skinny_pays(w_out, rows) and mid.stride(0) % 8 == 0 and mid.data_ptr() % 16 == 0):
+            ops.skinny_gemm_gated_residual(w_out, mid, x, gate, bias)  # few rows: gate and add ride in the last product
+            return
         delta = linear(mid, w_out, torch.float32)
-        ops.gated_residual_add(x, proj[:, gate_at:gate_at + self.width], bias, delta)
+        ops.gated_residual_add(x, gate, bias, delta)
 
     def forward(self, x: torch.Tensor, pending, batch, run: RunContext):
         if as_delta(pending) is not None:

@@ -375,6 +375,23 @@ def test_xielu_and_the_gated_residual_add(cuda_device, dtype):
     assert scaled_error(got, x.to(F) + pl.sigmoid(gate + bias.to(F)) * delta.to(F)) < 1e-6
 
 
+@pytest.mark.parametrize("rows,n,k", [(1, 64, 128), (8, 72, 200), (5, 256, 1024)])
+def test_the_gated_add_rides_in_the_last_product_of_a_decode_step(cuda_device, rows, n, k):
+    """x += sigmoid(gate + bias) * (a . W^T) by the decode product's epilogue against the same in float64."""
+    from models_b200.kernels import ops
+
+    gen = torch.Generator().manual_seed(rows + n)
+    a = torch.randn(rows, k, generator=gen).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=gen) * 0.1).to(torch.bfloat16)
+    x = torch.randn(rows, n, generator=gen)
+    wide = torch.randn(rows, n + 16, generator=gen).to(torch.bfloat16)  # the gate is a column slice
+    bias = torch.randn(n, generator=gen)
+    want = x.to(F) + pl.sigmoid(wide[:, 8:8 + n].to(F) + bias.to(F)) * (a.to(F) @ w.to(F).T)
+    got = x.to(cuda_device)
+    ops.skinny_gemm_gated_residual(w.to(cuda_device), a.to(cuda_device), got, wide.to(cuda_device)[:, 8:8 + n], bias.to(cuda_device))
+    assert scaled_error(got, want) < 2e-5
+
+
 # ----------------------------------------------------------------------------------- the model in the engine
 
 @pytest.mark.parametrize("dtype", DTYPES)
