@@ -200,7 +200,7 @@ gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __
                               int v_width, const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
                               const int* __restrict__ kv_lens, const float* __restrict__ head_bias, float* __restrict__ partial,
                               int span, int heads, int kv_heads, int head_dim, int value_dim, int page_size, float scale,
-                              float slope_exponent) {
+                              float slope_exponent, int staged) {
     grid_launch_dependents();
     grid_dependency_wait();
     extern __shared__ __align__(16) float decode_shared[];
@@ -216,6 +216,14 @@ gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __
     const int stride = 2 + value_dim;
     float* q_shared = decode_shared;
     float* meet = decode_shared + kGroup * head_dim;  // [warp][kGroup][stride]
+    // staged: a warp's chunk of 32 key rows (and value rows, where they are rows of their own) comes to shared memory in
+    // one batch of 16-byte copies, rows padded by 16 bytes, and is read from there as often as needed: one wait for
+    // memory per chunk.  (The rows of a chunk are neighbours in the pool: a chunk lies within a page.)
+    const bool own_values = v_pool != k_pool;
+    const int k_row_bytes = head_dim * (int)sizeof(T), v_row_bytes = v_width * (int)sizeof(T);
+    const int k_pad = k_row_bytes + 16, v_pad = v_row_bytes + 16;
+    unsigned char* k_staged = reinterpret_cast<unsigned char*>(meet + 4 * kGroup * stride) + (size_t)warp * 32 * (k_pad + (own_values ? v_pad : 0));
+    unsigned char* v_staged = own_values ? k_staged + 32 * k_pad : k_staged;
     if (begin >= end) {  // nothing of the sequence lies in this run (the whole block leaves)
         for (int g = threadIdx.x; g < count; g += blockDim.x) {
             float* dst = partial + (((size_t)seq * heads + head0 + g) * splits + split) * stride;
@@ -244,11 +252,32 @@ gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __
         const size_t base = (page * kv_heads + kv_head) * page_size + (chunk % page_size);
         const int p = chunk + lane;
         const bool visible = p < end;
+        if (staged) {
+            __syncwarp();  // the lanes are done with the chunk before
+            const unsigned char* k_src = reinterpret_cast<const unsigned char*>(k_pool + base * head_dim);
+            const uint32_t k_dst = (uint32_t)__cvta_generic_to_shared(k_staged);
+            const int k_pieces = k_row_bytes / 16;
+            for (int id = lane; id < 32 * k_pieces; id += 32) {
+                const int r = id / k_pieces, piece = id % k_pieces;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(k_dst + r * k_pad + piece * 16), "l"(k_src + (size_t)r * k_row_bytes + piece * 16));
+            }
+            if (own_values) {
+                const unsigned char* v_src = reinterpret_cast<const unsigned char*>(v_pool + base * v_width);
+                const uint32_t v_dst = (uint32_t)__cvta_generic_to_shared(v_staged);
+                const int v_pieces = v_row_bytes / 16;
+                for (int id = lane; id < 32 * v_pieces; id += 32) {
+                    const int r = id / v_pieces, piece = id % v_pieces;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(v_dst + r * v_pad + piece * 16), "l"(v_src + (size_t)r * v_row_bytes + piece * 16));
+                }
+            }
+            asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+            __syncwarp();
+        }
         float score[kGroup];
 #pragma unroll
         for (int g = 0; g < kGroup; ++g) score[g] = 0.0f;
         if (visible) {
-            const T* k_row = k_pool + (base + lane) * head_dim;
+            const T* k_row = staged ? reinterpret_cast<const T*>(k_staged + lane * k_pad) : k_pool + (base + lane) * head_dim;
             if (vector_ok) {
 #pragma unroll 8
                 for (int d = 0; d < head_dim; d += 8) {
@@ -298,7 +327,8 @@ gated_attention_decode_kernel(const T* __restrict__ q, int q_stride, const T* __
             float value[kAhead][kAcc];
 #pragma unroll
             for (int u = 0; u < kAhead; ++u) {
-                const T* v_row = v_pool + (base + min(j0 + u, last)) * v_width;
+                const int key = min(j0 + u, last);
+                const T* v_row = staged ? reinterpret_cast<const T*>(v_staged + key * (own_values ? v_pad : k_pad)) : v_pool + (base + key) * v_width;
 #pragma unroll
                 for (int i = 0; i < kAcc; ++i) value[u][i] = lane + 32 * i < value_dim ? Num<T>::load(v_row + lane + 32 * i) : 0.0f;
             }
@@ -633,7 +663,13 @@ int launch_decode(const void* q, int q_stride, void* out, int out_stride, const 
                   int value_dim, int page_size, float scale, float slope_exponent, int splits, int span, float* partial,
                   cudaStream_t stream) {
     const int group = heads / kv_heads, parts = (group + kGroup - 1) / kGroup;
-    const size_t smem = ((size_t)kGroup * head_dim + 4 * (size_t)kGroup * (2 + value_dim)) * sizeof(float);
+    size_t smem = ((size_t)kGroup * head_dim + 4 * (size_t)kGroup * (2 + value_dim)) * sizeof(float);
+    // a chunk per warp in shared memory where rows are whole 16-byte pieces and four chunks fit beside the rest
+    const size_t k_row = (size_t)head_dim * sizeof(T), v_row = (size_t)v_width * sizeof(T);
+    const size_t chunks = 4 * 32 * (k_row + 16 + (v_pool != k_pool ? v_row + 16 : 0));
+    const bool staged = k_row % 16 == 0 && v_row % 16 == 0 && !((uintptr_t)k_pool & 15) && !((uintptr_t)v_pool & 15) && smem % 16 == 0 &&
+                        smem + chunks <= 160 * 1024;
+    if (staged) smem += chunks;
     auto kernel = gated_attention_decode_kernel<T, kGroup, kAcc, kSoftmax>;
     if (smem > 48 * 1024) {
         cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -641,17 +677,20 @@ int launch_decode(const void* q, int q_stride, void* out, int out_stride, const 
     }
     MB_LAUNCH("gated_attention_decode", kernel, dim3(splits, kv_heads * parts, sequences), dim3(128), smem, stream, true, (const T*)q,
               q_stride, (const T*)k_pool, (const T*)v_pool, v_width, block_table, max_blocks, cu_q, kv_lens, head_bias, partial, span,
-              heads, kv_heads, head_dim, value_dim, page_size, scale, slope_exponent);
+              heads, kv_heads, head_dim, value_dim, page_size, scale, slope_exponent, staged ? 1 : 0);
     MB_LAUNCH("gated_attention_combine", (gated_attention_combine_kernel<T, kSoftmax>), dim3(heads, sequences),
               dim3((value_dim + 31) / 32 * 32), 0, stream, true, (const float*)partial, splits, (T*)out, out_stride, cu_q,
               (const T*)gate, gate_stride, gate_kind, heads, value_dim);
     return 0;
 }
 
+// Eight query heads per block only where that still leaves every multiprocessor several blocks: a warp's work is one long
+// chain of dependent steps, so with few sequences more and smaller blocks finish sooner although they read the rows twice.
 template <typename T, bool kSoftmax, typename... Args>
-int pick_decode(int group, int value_dim, Args... args) {
-    if (value_dim <= 128) return group <= 4 ? launch_decode<T, 4, 4, kSoftmax>(args...) : launch_decode<T, 8, 4, kSoftmax>(args...);
-    if (value_dim <= 256) return group <= 4 ? launch_decode<T, 4, 8, kSoftmax>(args...) : launch_decode<T, 8, 8, kSoftmax>(args...);
+int pick_decode(int group, int value_dim, bool many_blocks, Args... args) {
+    const bool four = group <= 4 || !many_blocks;
+    if (value_dim <= 128) return four ? launch_decode<T, 4, 4, kSoftmax>(args...) : launch_decode<T, 8, 4, kSoftmax>(args...);
+    if (value_dim <= 256) return four ? launch_decode<T, 4, 8, kSoftmax>(args...) : launch_decode<T, 8, 8, kSoftmax>(args...);
     return launch_decode<T, 4, 16, kSoftmax>(args...);
 }
 
@@ -680,9 +719,10 @@ MB_EXPORT int mb_gated_attention_decode(const void* q, int q_stride, void* out, 
     if (sequences > 65535 || heads > 65535) return fail("gated_attention_decode: %d sequences or %d heads exceed the grid limit 65535", sequences, heads);
     if (gate_kind < 0 || gate_kind > 2 || (gate_kind != 0 && gate == nullptr)) return fail("gated_attention_decode: gate kind %d", gate_kind);
     if (partial == nullptr) return fail("gated_attention_decode: no scratch memory");
+    const bool many_blocks = (long long)sequences * kv_heads * ((heads / kv_heads + 7) / 8) * splits >= 4 * 148;
     int status;
 #define MB_DECODE(T, S)                                                                                                          \
-    mb::pick_decode<T, S>(heads / kv_heads, value_dim, q, q_stride, out, out_stride, k_pool, v_pool, v_width, block_table,       \
+    mb::pick_decode<T, S>(heads / kv_heads, value_dim, many_blocks, q, q_stride, out, out_stride, k_pool, v_pool, v_width, block_table,       \
                           max_blocks, cu_q, kv_lens, head_bias, gate, gate_stride, gate_kind, sequences, heads, kv_heads, head_dim, \
                           value_dim, page_size, scale, slope_exponent, splits, span, partial, stream)
     if (dtype == MB_F32)
