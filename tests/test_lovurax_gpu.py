@@ -534,6 +534,35 @@ def test_long_decoding_from_graphs(cuda_device, folders, name, dtype):
     engine.cache.check()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("kind", ["retention", "attention", "latent"])
+def test_models_of_one_kind_of_layer(cuda_device, tmp_path, kind, dtype):
+    """Only retention layers (no cache group at all, state alone), only attention or only latent layers (no state, so
+    prompt steps are replayed from captures from their third occurrence on): prompts of one length class four times
+    over, then tokens one by one from captured decode steps."""
+    from models_b200.engine import StepEntry
+    from tiny_lovurax import attention, latent, retention
+
+    layers = {"retention": [retention(2, 16, 24, [0.9, 0.99], (8, 1e4), 48), retention(1, 32, 16, [0.95], None, None)],
+              "attention": [attention(4, 2, 16, 8, 0.25, (0.3, 16), 48), attention(2, 1, 32, 32, 0.2, None, None)],
+              "latent": [latent(2, 12, 20, 24, 0.3, 48), latent(4, 16, 16, 32, 0.25, None)]}[kind]
+    raw = {"architecture": "Lovurax", "vocab": 120, "width": 64, "norm": {"eps": 1e-5}, "logit_scale": 1.3, "layers": layers}
+    folder = make_folder(raw, 90, tmp_path)
+    engine = _engine(folder, dtype, 1024)
+    engine.enable_decode_graphs(4)
+    assert (engine.prompt_graphs is None) == (kind == "retention") and (len(engine.cache.groups) == 0) == (kind == "retention")
+    for seed in range(4):
+        tokens = random_tokens(120, 140, seed)
+        want = plain_logits(folder, tokens)
+        slot = engine.open_slot()
+        rows = [engine.step([StepEntry(slot, tokens[:100], [99])])]
+        for t in tokens[100:]:
+            rows.append(engine.decode([slot], [t]).clone())
+        assert scaled_error(torch.cat(rows), want[99:]) < TOLERANCE[dtype], seed
+        engine.release_slot(slot)
+    engine.cache.check()
+
+
 def test_logits_do_not_depend_on_the_batch_or_the_cut(cuda_device, folders):
     """float32: the same position through a whole prompt, through portions, and inside a batch differs by rounding only."""
     from models_b200.engine import StepEntry
