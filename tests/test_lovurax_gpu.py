@@ -449,7 +449,8 @@ def test_prompt_then_token_by_token(cuda_device, folders, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name,portions", [("A", [2, 3, 17, 64, 1, 2, 90, 21]), ("B", [64, 64, 2, 70]), ("C", [130, 2, 68])])
+@pytest.mark.parametrize("name,portions", [("A", [2, 3, 17, 64, 1, 2, 90, 21]), ("B", [64, 64, 2, 70]), ("C", [130, 2, 68]),
+                                           ("D", [5, 2, 2, 129, 62])])
 def test_prompt_in_portions(cuda_device, folders, name, portions, dtype):
     """A portion starts inside a sequence: its recurrence goes on from the stored state, its queries see the keys and
     latent rows of earlier portions, and its positions (rotation, temperature, distances) go on from where it stands."""

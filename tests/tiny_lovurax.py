@@ -58,7 +58,16 @@ LVX_C = {
                retention(4, 64, 128, [0.97, 0.99, 0.999, 0.9], (32, 100000.0), 512)],
 }
 
-LVX = {"A": LVX_A, "B": LVX_B, "C": LVX_C}
+# a width and head sizes that are no multiples of 8: no tensor-core product or attention takes them
+LVX_D = {
+    "architecture": "Lovurax", "vocab": 131, "width": 50, "norm": {"eps": 3e-6}, "logit_scale": 0.7,
+    "layers": [attention(3, 1, 18, 7, 0.22, (0.9, 3), 77),
+               latent(3, 10, 6, 22, 0.3, None),
+               retention(2, 18, 10, [0.9, 0.97], (6, 3000.0), 33),
+               attention(6, 3, 16, 16, 0.2, None, 40)],
+}
+
+LVX = {"A": LVX_A, "B": LVX_B, "C": LVX_C, "D": LVX_D}
 
 
 def make_folder(raw: dict, seed: int, root, std: float = 0.15) -> Path:
