@@ -29,6 +29,9 @@ constexpr int kSummarise = 1;  // a run from a zero state, no results: what it a
 constexpr int kEmit = 2;       // a run from its starting state in scratch [run], results written
 constexpr int kTokens = 8;     // tokens of a group: their inputs are fetched together, their norms taken together
 
+// Bytes of a group's raw rows, rounded up to 16.
+__host__ __device__ inline size_t raw_row_bytes(int row, size_t element) { return ((size_t)kTokens * row * element + 15) / 16 * 16; }
+
 // grid (heads, sequences, runs); block: value_dim rounded up to a multiple of 32 (at most 1024; 256 with kDim > 0).
 // kDim > 0: head_dim is kDim and a thread keeps its column of S in registers (a column in shared memory costs two
 // shared-memory accesses per product, which is what bounds the kernel then); kDim 0: any head_dim, columns in shared memory.
@@ -45,7 +48,7 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
                       const float* __restrict__ sin_table, int rotary_dim, const float* __restrict__ decay, float key_scale,
                       float eps, float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu_q,
                       int heads, int head_dim, int value_dim, T* __restrict__ out, int out_stride, float out_scale,
-                      int run_length, float* __restrict__ scratch) {
+                      int run_length, float* __restrict__ scratch, int async_ok) {
     grid_launch_dependents();
     grid_dependency_wait();
     extern __shared__ __align__(16) float shared[];
@@ -58,7 +61,13 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
     const int row = 2 * head_dim + 2 * value_dim;  // a token's staged floats: q, k, v, g
     float* staged = shared;
     float* results = staged + 2 * kTokens * row;
-    float* S = results + kTokens * value_dim;  // (kDim 0 only)
+    // raw: the next group's rows as they lie in memory (storage type) and its rows of the rotation tables, copied by
+    // cp.async while the group before is walked
+    const int half_early = rotary_dim / 2;
+    T* raw = reinterpret_cast<T*>(results + kTokens * value_dim);
+    float* raw_cos = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(raw) + raw_row_bytes(row, sizeof(T)));
+    float* raw_sin = raw_cos + kTokens * half_early;
+    float* S = raw_sin + kTokens * half_early + ((4 - (2 * kTokens * half_early) % 4) % 4);  // (kDim 0 only)
     float column_kept[kDim > 0 ? kDim : 1];
     const int j = threadIdx.x;
     const bool live = j < value_dim;
@@ -111,13 +120,86 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
         }
     };
 
-    stage(0, min(kTokens, count), 0);
+    // The same in two steps, for rows that cp.async can copy (async_ok: every row and table row starts on 16 bytes and is
+    // whole 16-byte pieces): `issue` starts the copies of a group's raw rows and returns; `convert`, after they have
+    // arrived, turns them into the staged floats from shared memory.  The copies fly while the group before is walked.
+    auto issue = [&](int t0, int n) {
+        const int piece = 16 / (int)sizeof(T);
+        const int qk_pieces = head_dim / piece, v_pieces = value_dim / piece, token_pieces = 2 * qk_pieces + 2 * v_pieces;
+        const uint32_t raw_at = (uint32_t)__cvta_generic_to_shared(raw);
+        for (int id = threadIdx.x; id < n * token_pieces; id += blockDim.x) {
+            const int u = id / token_pieces, p = id % token_pieces;
+            const T* source;
+            int c;  // the piece's first coordinate in the staged row
+            if (p < 2 * qk_pieces) {
+                const bool is_key = p >= qk_pieces;
+                if (kMode == kSummarise && !is_key) continue;
+                const int d = (is_key ? p - qk_pieces : p) * piece;
+                source = (is_key ? k : q) + (size_t)head * head_dim + d;
+                c = (is_key ? head_dim : 0) + d;
+            } else {
+                const int pv = p - 2 * qk_pieces;
+                const bool is_gate = pv >= v_pieces;
+                if (kMode == kSummarise && is_gate) continue;
+                const int d = (is_gate ? pv - v_pieces : pv) * piece;
+                source = (is_gate ? g : v) + (size_t)head * value_dim + d;
+                c = 2 * head_dim + (is_gate ? value_dim : 0) + d;
+            }
+            source += (size_t)(first + t0 + u) * in_stride;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(raw_at + (uint32_t)((u * row + c) * sizeof(T))), "l"(source));
+        }
+        if (rotary_dim > 0) {
+            const int table_pieces = half / 4;
+            const uint32_t cos_at = (uint32_t)__cvta_generic_to_shared(raw_cos), sin_at = (uint32_t)__cvta_generic_to_shared(raw_sin);
+            for (int id = threadIdx.x; id < n * 2 * table_pieces; id += blockDim.x) {
+                const int u = id / (2 * table_pieces), p = id % (2 * table_pieces);
+                const bool is_sin = p >= table_pieces;
+                const int at = (is_sin ? p - table_pieces : p) * 4;
+                const float* source = (is_sin ? sin_table : cos_table) + (size_t)(position0 + t0 + u) * half + at;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((is_sin ? sin_at : cos_at) + (uint32_t)((u * half + at) * 4)), "l"(source));
+            }
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+    auto convert = [&](int n, int b) {
+        for (int c = threadIdx.x; c < row; c += blockDim.x) {
+            const bool is_qk = c < 2 * head_dim;
+            const bool is_key = is_qk && c >= head_dim;
+            const bool is_gate = !is_qk && c >= 2 * head_dim + value_dim;
+            if (kMode == kSummarise && ((is_qk && !is_key) || is_gate)) continue;
+            const int d = is_qk ? (is_key ? c - head_dim : c) : 0;
+            const bool rotated = is_qk && d < rotary_dim;
+            const int pair = d < half ? d : d - half;
+            const int other = c + (d < half ? half : -half);
+            const float sign = d < half ? -1.0f : 1.0f;
+            const float factor = is_key ? key_scale : 1.0f;
+#pragma unroll
+            for (int u = 0; u < kTokens; ++u) {
+                if (u >= n) break;
+                float value = Num<T>::load(raw + u * row + c);
+                if (rotated) value = value * raw_cos[u * half + pair] + sign * Num<T>::load(raw + u * row + other) * raw_sin[u * half + pair];
+                staged[(b * kTokens + u) * row + c] = value * factor;
+            }
+        }
+    };
+
+    if (async_ok) {
+        issue(0, min(kTokens, count));
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        __syncthreads();
+        convert(min(kTokens, count), 0);
+    } else {
+        stage(0, min(kTokens, count), 0);
+    }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     for (int t0 = 0; t0 < count; t0 += kTokens) {
         const int b = (t0 / kTokens) & 1;
         const int n = min(kTokens, count - t0);
         const float* group = staged + b * kTokens * row;
+        const bool more = t0 + kTokens < count;
+        const int n_next = more ? min(kTokens, count - t0 - kTokens) : 0;
+        if (async_ok && more) issue(t0 + kTokens, n_next);  // under way while this group is walked
         if (live) {
 #pragma unroll
             for (int u = 0; u < kTokens; ++u) {
@@ -156,8 +238,11 @@ retention_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
                 if (kMode != kSummarise) results[u * value_dim + j] = o;
             }
         }
-        if (t0 + kTokens < count) stage(t0 + kTokens, min(kTokens, count - t0 - kTokens), b ^ 1);  // the other buffer
-        __syncthreads();  // the group's o and the next group's inputs are in shared memory
+        if (!async_ok && more) stage(t0 + kTokens, n_next, b ^ 1);  // the other buffer
+        if (async_ok) asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        __syncthreads();  // the group's o and the next group's inputs (staged, or raw) are in shared memory
+        if (async_ok && more) convert(n_next, b ^ 1);
+        if (kMode == kSummarise && async_ok) __syncthreads();  // the next group's staged floats, before they are read
         if (kMode != kSummarise) {
             for (int u = warp; u < n; u += warps) {  // a warp per token: root mean square of the head's o, gate, store
                 const float* o_row = results + u * value_dim;
@@ -240,6 +325,12 @@ int launch_retention(const void* q, const void* k, const void* v, const void* g,
                      int out_stride, float out_scale, int max_q_len, int run_length, float* scratch, cudaStream_t stream, size_t smem) {
     const dim3 block((value_dim + 31) / 32 * 32);
     const int runs = (run_length > 0 && max_q_len > run_length) ? (max_q_len + run_length - 1) / run_length : 1;
+    // rows that cp.async can copy: every row and table row starts on 16 bytes and is whole 16-byte pieces
+    const size_t element = sizeof(T);
+    const int async_ok = ((size_t)in_stride * element) % 16 == 0 && ((size_t)head_dim * element) % 16 == 0 &&
+                         ((size_t)value_dim * element) % 16 == 0 && !((uintptr_t)q & 15) && !((uintptr_t)k & 15) && !((uintptr_t)v & 15) &&
+                         !((uintptr_t)g & 15) &&
+                         (rotary_dim == 0 || ((rotary_dim / 2) % 4 == 0 && !((uintptr_t)cos_table & 15) && !((uintptr_t)sin_table & 15)));
     if (smem > 48 * 1024) {
         cudaFuncSetAttribute(retention_scan_kernel<T, kWhole, kDim>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         cudaFuncSetAttribute(retention_scan_kernel<T, kSummarise, kDim>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -248,7 +339,8 @@ int launch_retention(const void* q, const void* k, const void* v, const void* g,
 #define MB_SCAN(MODE, RUNS)                                                                                                      \
     MB_LAUNCH("retention_scan", (retention_scan_kernel<T, MODE, kDim>), dim3(heads, sequences, RUNS), dim3(block), smem, stream, true,  \
               (const T*)q, (const T*)k, (const T*)v, (const T*)g, in_stride, positions, cos_table, sin_table, rotary_dim, decay,  \
-              key_scale, eps, state, slots, cu_q, heads, head_dim, value_dim, (T*)out, out_stride, out_scale, run_length, scratch)
+              key_scale, eps, state, slots, cu_q, heads, head_dim, value_dim, (T*)out, out_stride, out_scale, run_length, scratch, \
+              async_ok)
     if (runs == 1) {
         MB_SCAN(kWhole, 1);
         return 0;
@@ -292,7 +384,9 @@ MB_EXPORT int mb_retention_scan(const void* q, const void* k, const void* v, con
     if (sequences > 65535) return fail("retention_scan: %d sequences exceed the grid limit 65535", sequences);
     if (run_length > 0 && max_q_len > run_length && scratch == nullptr) return fail("retention_scan: runs need scratch memory");
     if (run_length > 0 && (max_q_len + run_length - 1) / run_length > 65535) return fail("retention_scan: too many runs");
-    const size_t smem_kept = ((size_t)2 * kTokens * (2 * head_dim + 2 * value_dim) + (size_t)kTokens * value_dim) * sizeof(float);
+    const size_t element = dtype == MB_F32 ? 4 : 2;
+    const size_t smem_kept = ((size_t)2 * kTokens * (2 * head_dim + 2 * value_dim) + (size_t)kTokens * value_dim) * sizeof(float) +
+                             raw_row_bytes(2 * head_dim + 2 * value_dim, element) + ((size_t)2 * kTokens * (rotary_dim / 2) + 4) * sizeof(float);
     const size_t smem = smem_kept + (size_t)head_dim * value_dim * sizeof(float);
     const bool kept = value_dim <= 256 && value_dim % 2 == 0 && (head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128);
     if (!kept && smem > 227 * 1024) return fail("retention_scan: a state of %d x %d floats exceeds a block's shared memory", head_dim, value_dim);
